@@ -1,0 +1,93 @@
+"""BCSRGraphConv and its autograd function (reference: layers/layer.py:28-191).
+
+``BCSRSPMMFunction`` computes ``A @ (X @ W)`` with the forward SpMM kernel and, in backward,
+``A^T @ dY`` with the same kernel on the graph's cached transposed BCSR (the reference scatters
+with float atomics over the forward graph, layers/layer.py:71-77), followed by the two dense
+products of layers/layer.py:86,90.  The layer itself is the reference's GraphSAGE-style
+``A (X W_neigh) + X_target W_self`` (layers/layer.py:143-191).
+"""
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+from torch.autograd import Function
+
+from .. import core
+from ..helper import record_spmm_time
+
+
+def _spmm_graph(graph, dense):
+    """A @ dense for a BCSRGraph, values cast (and cached) to the dense dtype, N padded to 8."""
+    dense = dense.contiguous()
+    vals = graph.values_as(dense.dtype)
+    n = dense.shape[1]
+    pad = (-n) % 8
+    if pad:
+        dense = F.pad(dense, (0, pad))
+    out = core.spmm_raw(graph.window_offset, graph.original_col_indices, vals, dense)
+    return out[:, :n] if pad else out
+
+
+class BCSRSPMMFunction(Function):
+    @staticmethod
+    def forward(ctx, graph, features, weight, warps_per_block):
+        x_mult_w = torch.matmul(features, weight)
+        if core._timing_enabled:
+            output, timing = core.spmm_tc(graph.window_offset, graph.original_col_indices,
+                                          graph.values_as(x_mult_w.dtype), x_mult_w.contiguous(),
+                                          warps_per_block)
+        else:
+            output, timing = _spmm_graph(graph, x_mult_w), 0.0
+        record_spmm_time(timing)
+        ctx.save_for_backward(features, weight)
+        ctx.graph = graph
+        ctx.warps_per_block = warps_per_block
+        return output
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        features, weight = ctx.saved_tensors
+        graph = ctx.graph
+        num_input_nodes = features.shape[0]
+        grad_output = grad_output.contiguous()
+        g_t = graph.transposed(num_input_nodes, dtype=grad_output.dtype)
+        grad_input_aggr = _spmm_graph(g_t, grad_output)[:num_input_nodes]
+        grad_features = grad_weight = None
+        if ctx.needs_input_grad[1]:
+            grad_features = torch.matmul(grad_input_aggr, weight.t())
+        if ctx.needs_input_grad[2]:
+            grad_weight = torch.matmul(features.t(), grad_input_aggr)
+        return None, grad_features, grad_weight, None
+
+
+class BCSRGraphConv(nn.Module):
+    """Aggregation only; activation, normalisation and dropout live in the model."""
+
+    def __init__(self, in_feats: int, out_feats: int, dropout: float = 0.5, warps_per_block: int = 8):
+        super().__init__()
+        self.in_feats = in_feats
+        self.out_feats = out_feats
+        self.warps_per_block = warps_per_block
+        self.weight_neigh = nn.Parameter(torch.empty(in_feats, out_feats))
+        self.weight_self = nn.Parameter(torch.empty(in_feats, out_feats))
+        self.reset_parameters()
+
+    def reset_parameters(self):
+        nn.init.xavier_uniform_(self.weight_neigh)
+        nn.init.xavier_uniform_(self.weight_self)
+
+    def forward(self, graph, features: torch.Tensor, features_target: torch.Tensor = None) -> torch.Tensor:
+        h_neigh = BCSRSPMMFunction.apply(graph, features, self.weight_neigh, self.warps_per_block)
+        target_rows = h_neigh.shape[0]
+        if features_target is not None:
+            h_in_self = features_target
+        elif features.shape[0] >= target_rows:
+            h_in_self = features[:target_rows]          # target nodes first
+        else:
+            h_in_self = F.pad(features, (0, 0, 0, target_rows - features.shape[0]))
+        h_self = torch.matmul(h_in_self, self.weight_self)
+        # the SpMM returns whole windows (W*16 rows); trim or pad to the self path
+        if h_neigh.shape[0] > h_self.shape[0]:
+            h_neigh = h_neigh[:h_self.shape[0]]
+        elif h_neigh.shape[0] < h_self.shape[0]:
+            h_neigh = F.pad(h_neigh, (0, 0, 0, h_self.shape[0] - h_neigh.shape[0]))
+        return h_neigh + h_self

@@ -1,0 +1,122 @@
+/*
+ * grws_b200.h -- C ABI of libgrws_b200.so, the sm_100a replacement for Graph_RWS's native
+ * extension `core_lib` (core/wrapper/bind.cpp:78-161).
+ *
+ * Conventions, all entry points:
+ *   - plain pointers and sizes, no framework types; every array pointer is DEVICE memory unless
+ *     its comment says "host";
+ *   - the caller owns every buffer (inputs, outputs and scratch); nothing is allocated or freed
+ *     inside, nothing synchronises with the host, all work is queued on `stream`
+ *     (a cudaStream_t passed as void*), so calls are re-entrant and may come from several host
+ *     threads on several streams, as the reference's sampler thread does
+ *     (helper/engine.py:118-153);
+ *   - the return value is GRWS_OK (0) or a negative grws_status; grws_last_error() returns the
+ *     message of the calling thread's last failure.  The reference raises through TORCH_CHECK
+ *     (core/wrapper/spmm_wrapper.cu:48-51,89-90); the Python shim turns a negative status into
+ *     the same RuntimeError.
+ *
+ * BCSR layout (core/wrapper/convert_wrapper.cpp:27-180, data/bcsr.py:23-62):
+ *   window_offset        int64 [W+1]   prefix sum of tiles per 16-row window
+ *   original_col_indices int32 [T*8]   per window: sorted unique column ids, 8 per tile, -1 pad
+ *   values_condensed     [T*16*8]      per tile row-major [16][8]; fp32, fp16 or bf16
+ */
+#ifndef GRWS_B200_H
+#define GRWS_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define GRWS_TILE_ROWS 16
+#define GRWS_TILE_COLS 8
+
+typedef enum { GRWS_F32 = 0, GRWS_F16 = 1, GRWS_BF16 = 2 } grws_dtype;
+
+typedef enum {
+    GRWS_OK = 0,
+    GRWS_ERR_INVALID = -1,      /* bad argument (null pointer, negative size, misalignment)   */
+    GRWS_ERR_UNSUPPORTED = -2,  /* dtype / shape combination this build has no kernel for     */
+    GRWS_ERR_CUDA = -3,         /* a CUDA runtime call or launch failed                        */
+    GRWS_ERR_SCRATCH = -4,      /* caller-provided scratch or output buffer too small          */
+    GRWS_ERR_DEVICE = -5        /* a kernel reported a failure through its status word         */
+} grws_status;
+
+/* SpMM kernel selection. AUTO picks TCGEN05 when the shape allows it, else WARP_MMA. */
+typedef enum { GRWS_SPMM_AUTO = 0, GRWS_SPMM_WARP_MMA = 1, GRWS_SPMM_TCGEN05 = 2 } grws_spmm_algo;
+
+const char *grws_last_error(void);
+int grws_version(void);
+
+/* ------------------------------------------------------------------------------------------
+ * Forward SpMM  C[W*16, N] = A_bcsr * B[K, N].
+ * Replaces spmm_tc_wrapper + tcspmm_base_kernel (core/wrapper/spmm_wrapper.cu:33-95,
+ * core/include/spmm_tc.cuh:40-195).  Differences from the reference, all deliberate: every one
+ * of the N columns is computed (the reference computes 8*warps_per_block of them), values and
+ * B may be fp16/bf16 as well as fp32 (fp32 operands are rounded to TF32 like the reference,
+ * spmm_tc.cuh:118-121,144-145), accumulation is fp32, there is no host synchronisation.
+ * Column ids equal to -1 contribute nothing (spmm_tc.cuh:131-141); all others must be < K.
+ *   num_tiles_bound : any upper bound on window_offset[W] known to the host without a sync,
+ *                     e.g. the allocated tile count of `cols`;
+ *   val_dtype must equal b_dtype; N % 8 == 0; ldb, ldc in elements, rows 16-byte aligned;
+ *   scratch : grws_spmm_scratch_bytes(...) bytes, contents need not be initialised.
+ * The same entry point computes the backward product A^T * G when given the cached transposed
+ * BCSR built by grws_bcsr_transpose_* (this replaces the reference's atomic scatter
+ * spmm_transpose_wrapper + spmm_bcsr_transpose_atomic_kernel, spmm_wrapper.cu:109-152,
+ * spmm_tc.cuh:211-270).
+ * ------------------------------------------------------------------------------------------ */
+size_t grws_spmm_scratch_bytes(int64_t num_windows, int64_t num_tiles_bound, int64_t N, int algo);
+
+int grws_spmm_fwd(const int64_t *window_offset, const int32_t *cols, const void *vals,
+                  int val_dtype, const void *B, int b_dtype, int64_t ldb, void *C, int c_dtype,
+                  int64_t ldc, int64_t num_windows, int64_t num_tiles_bound, int64_t K, int64_t N,
+                  void *scratch, size_t scratch_bytes, int algo, void *stream);
+
+/* ------------------------------------------------------------------------------------------
+ * CSR -> BCSR on the device, two phases so that the caller can allocate exact outputs.
+ * Replaces csr_to_bcsr_cpu (core/wrapper/convert_wrapper.cpp:27-180; called from
+ * data/bcsr.py:209-216) and produces bit-identical arrays: per window the sorted unique
+ * column ids, 8 per tile, -1 padding, values [tile][16][8] with zeros where there is no edge,
+ * the last duplicate of a (row, column) pair winning.
+ *   count: writes window_offset [ceil(num_rows/16)+1]; the caller then reads its last entry
+ *          (the tile count T) and allocates out_cols [T*8], out_vals [T*128];
+ *   fill : must get the same scratch buffer, untouched since the count call.
+ * row_ptr int64 [num_rows+1], col_idx int32 [nnz] (0 <= id), values fp32 [nnz]; nnz < 2^31.
+ * ------------------------------------------------------------------------------------------ */
+size_t grws_csr_to_bcsr_scratch_bytes(int64_t num_rows, int64_t nnz);
+
+int grws_csr_to_bcsr_count(int64_t num_rows, const int64_t *row_ptr, const int32_t *col_idx,
+                           const float *values, int64_t nnz, int64_t *window_offset, void *scratch,
+                           size_t scratch_bytes, void *stream);
+
+int grws_csr_to_bcsr_fill(int64_t num_rows, int64_t nnz, const int64_t *window_offset,
+                          int64_t num_tiles, int32_t *out_cols, void *out_vals, int val_dtype,
+                          void *scratch, size_t scratch_bytes, void *stream);
+
+/* ------------------------------------------------------------------------------------------
+ * BCSR -> CSR of the transposed matrix (rows = the BCSR's column ids), the first half of
+ * building the cached transposed BCSR that the backward product runs on.  The reference has
+ * no such structure: its backward is an atomicAdd scatter over the forward graph
+ * (core/include/spmm_tc.cuh:211-270, called from layers/layer.py:71-77).  Entries with a -1
+ * column id, an id >= num_cols or a zero value are dropped, like spmm_tc.cuh:258,264.
+ *   count: writes row_ptr_t int64 [num_cols+1]; the caller reads its last entry (nnz);
+ *   fill : writes out_col int32 [nnz] (row ids of A) and out_val fp32 [nnz]; the order of the
+ *          entries inside one row is unspecified (grws_csr_to_bcsr_* sorts them).
+ * ------------------------------------------------------------------------------------------ */
+size_t grws_bcsr_transpose_scratch_bytes(int64_t num_cols);
+
+int grws_bcsr_transpose_count(const int64_t *window_offset, const int32_t *cols, const void *vals,
+                              int val_dtype, int64_t num_windows, int64_t num_cols,
+                              int64_t *row_ptr_t, void *scratch, size_t scratch_bytes, void *stream);
+
+int grws_bcsr_transpose_fill(const int64_t *window_offset, const int32_t *cols, const void *vals,
+                             int val_dtype, int64_t num_windows, int64_t num_cols,
+                             const int64_t *row_ptr_t, int32_t *out_col, float *out_val,
+                             void *scratch, size_t scratch_bytes, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GRWS_B200_H */

@@ -1,0 +1,116 @@
+"""GPU parity of the forward / transposed SpMM against the CPU checker, through the C ABI."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import GOLDEN, golden_cases, load_case
+from gpu_util import DT, check_spmm_tolerance
+
+pytestmark = pytest.mark.gpu
+
+
+def _run(oracle, wo, cols, vals_np, num_cols, N, dt, algo, seed=0):
+    from graph_rws_b200 import core
+    dev = torch.device("cuda")
+    dtype = DT[dt]
+    g = torch.Generator().manual_seed(seed)
+    B = torch.randn(num_cols, N, generator=g).to(dtype)
+    vals = torch.from_numpy(vals_np).to(dtype)
+    C = core.spmm_raw(torch.from_numpy(wo).to(dev), torch.from_numpy(cols).to(dev), vals.to(dev), B.to(dev),
+                      algo=algo)
+    torch.cuda.synchronize()
+    C_ref = oracle.spmm_fwd(wo, cols, vals.float().numpy(), B.float().numpy())
+    return C.float().cpu().numpy(), C_ref
+
+
+@pytest.mark.parametrize("dt", ["f32", "f16", "bf16"])
+@pytest.mark.parametrize("path", golden_cases(), ids=lambda p: os.path.basename(p)[5:-4])
+def test_warp_mma_matches_oracle_on_golden_graphs(oracle, path, dt):
+    from graph_rws_b200 import core
+    c = load_case(path)
+    num_cols = int(c["col_idx"].max()) + 1 if c["col_idx"].size else 8
+    for N in (8, 72, 128):
+        C, C_ref = _run(oracle, c["window_offset"], c["cols"], c["vals"], num_cols, N, dt, core.ALGO_WARP_MMA)
+        assert C.shape == C_ref.shape
+        check_spmm_tolerance(C, C_ref, None, f"{os.path.basename(path)} N={N} {dt}")
+
+
+@pytest.mark.parametrize("dt,N", [("f16", 128), ("bf16", 256), ("f32", 16), ("f32", 136), ("f16", 64)])
+def test_warp_mma_power_law_graph_with_split_windows(oracle, dt, N):
+    """A hub-heavy graph: windows longer than the split threshold exercise the partial-sum path."""
+    from graph_rws_b200 import core
+    from graph_rws_b200.data import synthetic
+    g = synthetic.sym_normalized_csr(6000, *synthetic.chung_lu_edges(6000, 90000, 2.1, 21))
+    wo, cols, vals = oracle.csr_to_bcsr(g.num_nodes, g.row_ptr, g.col_idx, g.values)
+    assert (np.diff(wo) > 128).any(), "test graph must contain windows that get split"
+    C, C_ref = _run(oracle, wo, cols, vals, g.num_nodes, N, dt, core.ALGO_WARP_MMA, seed=5)
+    check_spmm_tolerance(C, C_ref, None, f"power-law N={N} {dt}")
+
+
+def test_padding_columns_contribute_nothing(oracle):
+    """-1 column ids are masked even when their value slots hold non-zero data."""
+    from graph_rws_b200 import core
+    c = load_case(os.path.join(GOLDEN, "bcsr_ragged_37x50.npz"))
+    vals = c["vals"].copy().reshape(-1, 16, 8)
+    pad = (c["cols"].reshape(-1, 8) == -1)
+    assert pad.any()
+    vals[np.broadcast_to(pad[:, None, :], vals.shape)] = 123.0
+    C, _ = _run(oracle, c["window_offset"], c["cols"], vals.reshape(-1), 50, 64, "f16", core.ALGO_WARP_MMA)
+    _, C_ref = _run(oracle, c["window_offset"], c["cols"], c["vals"], 50, 64, "f16", core.ALGO_WARP_MMA)
+    check_spmm_tolerance(C, C_ref, None, "padding")
+
+
+def test_reference_named_entry_points(oracle):
+    """spmm_tc / spmm_transpose keep the reference's signatures (core/wrapper/bind.cpp:124-140)."""
+    from graph_rws_b200 import core
+    c = load_case(os.path.join(GOLDEN, "bcsr_chunglu_600.npz"))
+    dev = torch.device("cuda")
+    wo, cols = torch.from_numpy(c["window_offset"]).to(dev), torch.from_numpy(c["cols"]).to(dev)
+    vals = torch.from_numpy(c["vals"]).to(dev)
+    B = torch.randn(600, 7, device=dev)                       # N = 7: padded inside
+    C, ms = core.spmm_tc(wo, cols, vals, B, 8)
+    assert C.shape == (38 * 16, 7) and C.dtype == torch.float32 and ms == 0.0
+    C_ref = oracle.spmm_fwd(c["window_offset"], c["cols"], c["vals"], B.cpu().numpy())
+    check_spmm_tolerance(C.cpu().numpy(), C_ref, None, "spmm_tc")
+    G = torch.randn(38 * 16, 24, device=dev)
+    Gin = core.spmm_transpose(wo, cols, vals, G, 600)
+    assert Gin.shape == (600, 24)
+    Gin_ref = oracle.spmm_transpose(c["window_offset"], c["cols"], c["vals"], G.cpu().numpy(), 600)
+    check_spmm_tolerance(Gin.cpu().numpy(), Gin_ref, None, "spmm_transpose")
+    # second call hits the cached transposed graph and is bit-identical (no atomics)
+    assert torch.equal(core.spmm_transpose(wo, cols, vals, G, 600), Gin)
+    with pytest.raises(RuntimeError):
+        core.spmm_tc(wo, cols, vals, B.cpu(), 8)
+    with pytest.raises(RuntimeError):
+        core.spmm_tc(wo, cols, vals, B.t(), 8)
+    core.set_spmm_timing(True)
+    try:
+        _, ms = core.spmm_tc(wo, cols, vals, B, 8)
+        assert ms > 0.0
+    finally:
+        core.set_spmm_timing(False)
+
+
+def test_against_reference_kernels_when_built(oracle):
+    """Same inputs through the reference's own CUDA kernels (compiled into oracle/_ref/):
+    spmm_tc with warps_per_block = N/8 (it computes 8 columns per warp) and spmm_transpose."""
+    from oracle import build_ref
+    from graph_rws_b200 import core
+    ref = build_ref.load()
+    if ref is None:
+        pytest.skip("oracle/_ref/core_lib.so not built")
+    c = load_case(os.path.join(GOLDEN, "bcsr_chunglu_600.npz"))
+    dev = torch.device("cuda")
+    wo, cols = torch.from_numpy(c["window_offset"]).to(dev), torch.from_numpy(c["cols"]).to(dev)
+    vals = torch.from_numpy(c["vals"]).to(dev)
+    for N in (64, 128, 256):
+        B = torch.randn(600, N, device=dev)
+        C_theirs, _ = ref.spmm_tc(wo, cols, vals, B, N // 8)
+        C_ours, _ = core.spmm_tc(wo, cols, vals, B, N // 8)
+        check_spmm_tolerance(C_ours.cpu().numpy(), C_theirs.cpu().numpy(), None, f"vs reference spmm_tc N={N}")
+    G = torch.randn(38 * 16, 64, device=dev)
+    G_theirs = ref.spmm_transpose(wo, cols, vals, G, 600)
+    G_ours = core.spmm_transpose(wo, cols, vals, G, 600)
+    check_spmm_tolerance(G_ours.cpu().numpy(), G_theirs.cpu().numpy(), None, "vs reference spmm_transpose")
