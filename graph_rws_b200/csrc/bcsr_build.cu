@@ -28,7 +28,7 @@ struct BuildScratch {
     uint64_t *keys_a, *keys_b;
     float *vals_a, *vals_b;
     int32_t *flags;         // per sorted entry: 1 when it opens a new (window, column) run
-    int32_t *uidx;          // per sorted entry: global index of its (window, column) slot
+    int32_t *uidx;          // per sorted entry: 1 + global index of its (window, column) slot (inclusive scan of flags)
     int32_t *nuniq;         // [W+2] unique columns per window
     int32_t *ufirst;        // [W+2] exclusive scan of nuniq
     int64_t *tiles;         // [W+2] tiles per window, shifted by one
@@ -41,7 +41,7 @@ static size_t cub_temp_bytes(int64_t nnz, int64_t W) {
     size_t s1 = 0, s2 = 0, s3 = 0;
     cub::DeviceRadixSort::SortPairs(nullptr, s1, (const uint64_t *)nullptr, (uint64_t *)nullptr,
                                     (const float *)nullptr, (float *)nullptr, (int)nnz, 0, 64);
-    cub::DeviceScan::ExclusiveSum(nullptr, s2, (const int32_t *)nullptr, (int32_t *)nullptr, (int)nnz);
+    cub::DeviceScan::InclusiveSum(nullptr, s2, (const int32_t *)nullptr, (int32_t *)nullptr, (int)nnz);
     cub::DeviceScan::InclusiveSum(nullptr, s3, (const int64_t *)nullptr, (int64_t *)nullptr, (int)(W + 1));
     size_t m = s1 > s2 ? s1 : s2;
     return m > s3 ? m : s3;
@@ -114,7 +114,7 @@ __global__ void fill_kernel(int64_t nnz, const uint64_t *__restrict__ keys, cons
     const int64_t w = (int64_t)(key >> (32 + ROW_BITS));
     const int32_t col = (int32_t)((key >> ROW_BITS) & 0xffffffffu);
     const int r = (int)(key & (TILE_ROWS - 1));
-    const int32_t slot = uidx[i] - ufirst[w];
+    const int32_t slot = uidx[i] - 1 - ufirst[w];
     const int64_t tile = window_offset[w] + slot / TILE_COLS;
     const int ic = slot % TILE_COLS;
     out_cols[tile * TILE_COLS + ic] = col;                    // every entry of the run writes the same id
@@ -218,7 +218,7 @@ int grws_csr_to_bcsr_count(int64_t num_rows, const int64_t *row_ptr, const int32
                                                       (int)nnz, 0, end_bit, st));
         head_flags_kernel<<<blocks_for(nnz, 256), 256, 0, st>>>(nnz, s.keys_b, s.flags, s.nuniq);
         tmp = s.cub_bytes;
-        GRWS_CUDA_TRY(cub::DeviceScan::ExclusiveSum(s.cub_tmp, tmp, s.flags, s.uidx, (int)nnz, st));
+        GRWS_CUDA_TRY(cub::DeviceScan::InclusiveSum(s.cub_tmp, tmp, s.flags, s.uidx, (int)nnz, st));
     }
     tiles_kernel<<<blocks_for(W + 1, 256), 256, 0, st>>>(W, s.nuniq, s.tiles);
     size_t tmp = s.cub_bytes;

@@ -11,6 +11,8 @@
 //   - fp16/bf16 use m16n8k16 over a pair of tiles, fp32 is rounded to TF32 (cvt.rna, as
 //     spmm_tc.cuh:118-121,144-145 does) and uses m16n8k8 over one tile; accumulation is fp32;
 //   - loads of the next two steps are in flight while the current one is multiplied.
+#include <stdlib.h>
+
 #include "grws_common.cuh"
 
 namespace grws {
@@ -29,11 +31,37 @@ struct SpmmWarpParams {
 
 constexpr int WARPS_PER_CTA = 8;
 
-__device__ __forceinline__ uint4 ldg128(const void *p) {
+// L2 residency hints: the gathered rows of B are re-read by many windows and should stay in L2
+// (evict_last); tile values, column ids and the output are touched once (evict_first).
+__device__ __forceinline__ uint64_t l2_policy_keep() {
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ uint64_t l2_policy_stream() {
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ uint4 ldg128_hint(const void *p, uint64_t pol) {
     uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    asm volatile("ld.global.nc.L1::no_allocate.L2::cache_hint.v4.u32 {%0,%1,%2,%3}, [%4], %5;"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p), "l"(pol));
     return v;
+}
+__device__ __forceinline__ uint32_t ldg32_hint(const void *p, uint64_t pol) {
+    uint32_t v;
+    asm volatile("ld.global.nc.L1::no_allocate.L2::cache_hint.u32 %0, [%1], %2;" : "=r"(v) : "l"(p), "l"(pol));
+    return v;
+}
+__device__ __forceinline__ int2 ldg64_hint(const void *p, uint64_t pol) {
+    int2 v;
+    asm volatile("ld.global.nc.L1::no_allocate.L2::cache_hint.v2.s32 {%0,%1}, [%2], %3;" : "=r"(v.x), "=r"(v.y) : "l"(p), "l"(pol));
+    return v;
+}
+__device__ __forceinline__ void stg128_hint(void *p, uint4 v, uint64_t pol) {
+    asm volatile("st.global.L2::cache_hint.v4.u32 [%0], {%1,%2,%3,%4}, %5;"
+                 :: "l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w), "l"(pol) : "memory");
 }
 
 __device__ __forceinline__ uint32_t to_tf32(uint32_t f32_bits) {
@@ -81,22 +109,22 @@ struct StepCols {
 // column ids of step `p` of the segment starting at tile `seg_s` (tiles [seg_s, seg_e))
 template <int DT>
 __device__ __forceinline__ StepCols load_cols(const int32_t *__restrict__ cols, int64_t seg_s,
-                                              int64_t seg_e, int64_t p, int t) {
+                                              int64_t seg_e, int64_t p, int t, uint64_t pol) {
     using G = StepGeom<DT>;
     StepCols sc;
     const int64_t tile0 = seg_s + p * G::kTiles;
     if constexpr (G::kHalf) {
         // rows k = 2t, 2t+1 (first tile) and 8+2t, 9+2t (second tile)
         int2 lo = make_int2(-1, -1), hi = make_int2(-1, -1);
-        if (tile0 < seg_e) lo = __ldg(reinterpret_cast<const int2 *>(cols + tile0 * TILE_COLS + 2 * t));
-        if (tile0 + 1 < seg_e) hi = __ldg(reinterpret_cast<const int2 *>(cols + (tile0 + 1) * TILE_COLS + 2 * t));
+        if (tile0 < seg_e) lo = ldg64_hint(cols + tile0 * TILE_COLS + 2 * t, pol);
+        if (tile0 + 1 < seg_e) hi = ldg64_hint(cols + (tile0 + 1) * TILE_COLS + 2 * t, pol);
         sc.c[0] = lo.x; sc.c[1] = lo.y; sc.c[2] = hi.x; sc.c[3] = hi.y;
     } else {
         // rows k = t and t + 4 of the single tile
         sc.c[0] = sc.c[1] = sc.c[2] = sc.c[3] = -1;
         if (tile0 < seg_e) {
-            sc.c[0] = __ldg(cols + tile0 * TILE_COLS + t);
-            sc.c[1] = __ldg(cols + tile0 * TILE_COLS + t + 4);
+            sc.c[0] = (int)ldg32_hint(cols + tile0 * TILE_COLS + t, pol);
+            sc.c[1] = (int)ldg32_hint(cols + tile0 * TILE_COLS + t + 4, pol);
         }
     }
     return sc;
@@ -106,7 +134,8 @@ template <int DT, int NG>
 __device__ __forceinline__ void load_step(StepData<DT, NG> &d, const StepCols &sc,
                                           const void *__restrict__ vals, const void *__restrict__ B,
                                           int64_t ldb, int64_t N, int64_t n0, int64_t seg_s,
-                                          int64_t seg_e, int64_t p, int g, int t) {
+                                          int64_t seg_e, int64_t p, int g, int t, uint64_t keep,
+                                          uint64_t stream) {
     using G = StepGeom<DT>;
     const char *Bb = static_cast<const char *>(B);
 #pragma unroll
@@ -115,7 +144,7 @@ __device__ __forceinline__ void load_step(StepData<DT, NG> &d, const StepCols &s
         for (int gi = 0; gi < NG; ++gi) {
             const int64_t feat = n0 + gi * G::kGroup + g * (16 / G::kElem);
             uint4 v = make_uint4(0u, 0u, 0u, 0u);
-            if (sc.c[r] >= 0 && feat < N) v = ldg128(Bb + ((int64_t)sc.c[r] * ldb + feat) * G::kElem);
+            if (sc.c[r] >= 0 && feat < N) v = ldg128_hint(Bb + ((int64_t)sc.c[r] * ldb + feat) * G::kElem, keep);
             d.h[r * NG + gi] = v;
         }
     }
@@ -125,19 +154,19 @@ __device__ __forceinline__ void load_step(StepData<DT, NG> &d, const StepCols &s
     if constexpr (G::kHalf) {
         // 16-bit tile: row r is 16 bytes = 4 words; a0 = (row g, k 2t..2t+1), a1 = (row g+8, same k)
         if (tile0 < seg_e) {
-            d.a[0] = __ldg(v32 + tile0 * (TILE_ELEMS / 2) + g * 4 + t);
-            d.a[1] = __ldg(v32 + tile0 * (TILE_ELEMS / 2) + (g + 8) * 4 + t);
+            d.a[0] = ldg32_hint(v32 + tile0 * (TILE_ELEMS / 2) + g * 4 + t, stream);
+            d.a[1] = ldg32_hint(v32 + tile0 * (TILE_ELEMS / 2) + (g + 8) * 4 + t, stream);
         }
         if (tile0 + 1 < seg_e) {
-            d.a[2] = __ldg(v32 + (tile0 + 1) * (TILE_ELEMS / 2) + g * 4 + t);
-            d.a[3] = __ldg(v32 + (tile0 + 1) * (TILE_ELEMS / 2) + (g + 8) * 4 + t);
+            d.a[2] = ldg32_hint(v32 + (tile0 + 1) * (TILE_ELEMS / 2) + g * 4 + t, stream);
+            d.a[3] = ldg32_hint(v32 + (tile0 + 1) * (TILE_ELEMS / 2) + (g + 8) * 4 + t, stream);
         }
     } else {
         if (tile0 < seg_e) {
-            d.a[0] = __ldg(v32 + tile0 * TILE_ELEMS + g * 8 + t);
-            d.a[1] = __ldg(v32 + tile0 * TILE_ELEMS + (g + 8) * 8 + t);
-            d.a[2] = __ldg(v32 + tile0 * TILE_ELEMS + g * 8 + t + 4);
-            d.a[3] = __ldg(v32 + tile0 * TILE_ELEMS + (g + 8) * 8 + t + 4);
+            d.a[0] = ldg32_hint(v32 + tile0 * TILE_ELEMS + g * 8 + t, stream);
+            d.a[1] = ldg32_hint(v32 + tile0 * TILE_ELEMS + (g + 8) * 8 + t, stream);
+            d.a[2] = ldg32_hint(v32 + tile0 * TILE_ELEMS + g * 8 + t + 4, stream);
+            d.a[3] = ldg32_hint(v32 + tile0 * TILE_ELEMS + (g + 8) * 8 + t + 4, stream);
         }
     }
 }
@@ -189,13 +218,15 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
 // store `count` consecutive outputs (count = 2 * kSlabs) of one row; v[i] is feature feat0 + i
 template <int COUNT>
 __device__ __forceinline__ void store_row(void *C, int c_dtype, int64_t elem_off, int64_t feat0,
-                                          int64_t N, const float (&v)[COUNT]) {
+                                          int64_t N, const float (&v)[COUNT], uint64_t pol) {
     if (feat0 >= N) return;   // N is a multiple of 8 and feat0 of COUNT (8 or 16): all or nothing per 8
     if (c_dtype == GRWS_F32) {
         float4 *p = reinterpret_cast<float4 *>(static_cast<float *>(C) + elem_off);
 #pragma unroll
         for (int i = 0; i < COUNT / 4; ++i)
-            if (feat0 + 4 * i < N) p[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+            if (feat0 + 4 * i < N)
+                stg128_hint(p + i, make_uint4(__float_as_uint(v[4 * i]), __float_as_uint(v[4 * i + 1]),
+                                              __float_as_uint(v[4 * i + 2]), __float_as_uint(v[4 * i + 3])), pol);
     } else {
         uint4 *p = reinterpret_cast<uint4 *>(static_cast<uint16_t *>(C) + elem_off);
 #pragma unroll
@@ -209,7 +240,7 @@ __device__ __forceinline__ void store_row(void *C, int c_dtype, int64_t elem_off
                 o.x = pack_bf16(v[8 * i], v[8 * i + 1]); o.y = pack_bf16(v[8 * i + 2], v[8 * i + 3]);
                 o.z = pack_bf16(v[8 * i + 4], v[8 * i + 5]); o.w = pack_bf16(v[8 * i + 6], v[8 * i + 7]);
             }
-            p[i] = o;
+            stg128_hint(p + i, o, pol);
         }
     }
 }
@@ -225,6 +256,7 @@ spmm_warp_kernel(const SpmmWarpParams prm) {
     const int64_t n0 = (int64_t)blockIdx.y * (NG * G::kGroup);
     const int64_t W = prm.W, N = prm.N;
     const int64_t T = __ldg(prm.window_offset + W);
+    const uint64_t keep = l2_policy_keep(), stream = l2_policy_stream();
 
     int64_t w_first, w_unused;
     const int64_t s = warp_cut(prm.window_offset, W, T, item, prm.n_items, prm.chunk, prm.long_window, lane, &w_first);
@@ -245,22 +277,22 @@ spmm_warp_kernel(const SpmmWarpParams prm) {
                 for (int i = 0; i < 4; ++i) acc[gi][j][i] = 0.f;
 
         if (nsteps > 0) {
-            StepCols c2 = load_cols<DT>(prm.cols, seg_s, seg_e, 2, t);
-            StepCols c3 = load_cols<DT>(prm.cols, seg_s, seg_e, 3, t);
+            StepCols c2 = load_cols<DT>(prm.cols, seg_s, seg_e, 2, t, stream);
+            StepCols c3 = load_cols<DT>(prm.cols, seg_s, seg_e, 3, t, stream);
             StepData<DT, NG> d0, d1;
             {
-                StepCols c0 = load_cols<DT>(prm.cols, seg_s, seg_e, 0, t);
-                StepCols c1 = load_cols<DT>(prm.cols, seg_s, seg_e, 1, t);
-                load_step<DT, NG>(d0, c0, prm.vals, prm.B, prm.ldb, N, n0, seg_s, seg_e, 0, g, t);
-                load_step<DT, NG>(d1, c1, prm.vals, prm.B, prm.ldb, N, n0, seg_s, seg_e, 1, g, t);
+                StepCols c0 = load_cols<DT>(prm.cols, seg_s, seg_e, 0, t, stream);
+                StepCols c1 = load_cols<DT>(prm.cols, seg_s, seg_e, 1, t, stream);
+                load_step<DT, NG>(d0, c0, prm.vals, prm.B, prm.ldb, N, n0, seg_s, seg_e, 0, g, t, keep, stream);
+                load_step<DT, NG>(d1, c1, prm.vals, prm.B, prm.ldb, N, n0, seg_s, seg_e, 1, g, t, keep, stream);
             }
             for (int64_t p = 0; p < nsteps; p += 2) {
-                StepCols c4 = load_cols<DT>(prm.cols, seg_s, seg_e, p + 4, t);
-                StepCols c5 = load_cols<DT>(prm.cols, seg_s, seg_e, p + 5, t);
+                StepCols c4 = load_cols<DT>(prm.cols, seg_s, seg_e, p + 4, t, stream);
+                StepCols c5 = load_cols<DT>(prm.cols, seg_s, seg_e, p + 5, t, stream);
                 mma_step<DT, NG>(acc, d0);
-                load_step<DT, NG>(d0, c2, prm.vals, prm.B, prm.ldb, N, n0, seg_s, seg_e, p + 2, g, t);
+                load_step<DT, NG>(d0, c2, prm.vals, prm.B, prm.ldb, N, n0, seg_s, seg_e, p + 2, g, t, keep, stream);
                 if (p + 1 < nsteps) mma_step<DT, NG>(acc, d1);
-                load_step<DT, NG>(d1, c3, prm.vals, prm.B, prm.ldb, N, n0, seg_s, seg_e, p + 3, g, t);
+                load_step<DT, NG>(d1, c3, prm.vals, prm.B, prm.ldb, N, n0, seg_s, seg_e, p + 3, g, t, keep, stream);
                 c2 = c4;
                 c3 = c5;
             }
@@ -279,12 +311,12 @@ spmm_warp_kernel(const SpmmWarpParams prm) {
             }
             const int64_t feat0 = n0 + gi * G::kGroup + t * (2 * G::kSlabs);
             if (!head && !tail) {
-                store_row<2 * G::kSlabs>(prm.C, prm.c_dtype, (w * TILE_ROWS + g) * prm.ldc + feat0, feat0, N, lo);
-                store_row<2 * G::kSlabs>(prm.C, prm.c_dtype, (w * TILE_ROWS + g + 8) * prm.ldc + feat0, feat0, N, hi);
+                store_row<2 * G::kSlabs>(prm.C, prm.c_dtype, (w * TILE_ROWS + g) * prm.ldc + feat0, feat0, N, lo, stream);
+                store_row<2 * G::kSlabs>(prm.C, prm.c_dtype, (w * TILE_ROWS + g + 8) * prm.ldc + feat0, feat0, N, hi, stream);
             } else {
                 float *slot = prm.partial + (2 * item + (tail ? 1 : 0)) * (TILE_ROWS * N);
-                store_row<2 * G::kSlabs>(slot, GRWS_F32, (int64_t)g * N + feat0, feat0, N, lo);
-                store_row<2 * G::kSlabs>(slot, GRWS_F32, (int64_t)(g + 8) * N + feat0, feat0, N, hi);
+                store_row<2 * G::kSlabs>(slot, GRWS_F32, (int64_t)g * N + feat0, feat0, N, lo, stream);
+                store_row<2 * G::kSlabs>(slot, GRWS_F32, (int64_t)(g + 8) * N + feat0, feat0, N, hi, stream);
             }
         }
     }
@@ -345,6 +377,12 @@ size_t spmm_warp_scratch_bytes(int64_t num_tiles_bound, int64_t N) {
     return (size_t)n_items * 2 * TILE_ROWS * (size_t)N * sizeof(float);
 }
 
+// GRWS_WARP_NARROW=1 gives every warp a single feature group (more warps per SM, A read per group)
+static bool narrow_slabs() {
+    static const int v = [] { const char *e = getenv("GRWS_WARP_NARROW"); return e ? atoi(e) : 0; }();
+    return v != 0;
+}
+
 template <int DT>
 static int launch_warp(const SpmmWarpParams &prm, cudaStream_t stream) {
     using G = StepGeom<DT>;
@@ -353,8 +391,9 @@ static int launch_warp(const SpmmWarpParams &prm, cudaStream_t stream) {
     const unsigned gx = (unsigned)ceil_div(prm.n_items, WARPS_PER_CTA);
     // features per warp: as many groups as keep the register budget (<= 128 features)
     constexpr int kMaxGroups = 128 / G::kGroup;   // 2 (16-bit) or 4 (fp32)
-    if (N <= G::kGroup) {
-        spmm_warp_kernel<DT, 1><<<dim3(gx, 1), block, 0, stream>>>(prm);
+    if (N <= G::kGroup || narrow_slabs()) {
+        const unsigned gy = (unsigned)ceil_div(N, G::kGroup);
+        spmm_warp_kernel<DT, 1><<<dim3(gx, gy), block, 0, stream>>>(prm);
     } else if (N <= 2 * G::kGroup || kMaxGroups == 2) {
         const unsigned gy = (unsigned)ceil_div(N, 2 * G::kGroup);
         spmm_warp_kernel<DT, 2><<<dim3(gx, gy), block, 0, stream>>>(prm);

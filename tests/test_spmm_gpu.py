@@ -11,15 +11,20 @@ from gpu_util import DT, check_spmm_tolerance
 pytestmark = pytest.mark.gpu
 
 
-def _run(oracle, wo, cols, vals_np, num_cols, N, dt, algo, seed=0):
+def _run(oracle, wo, cols, vals_np, num_cols, N, dt, algo, seed=0, out_dtype=None):
+    """bf16 operands are checked with an fp32 output: the stated tolerance (relative Frobenius
+    1e-3) is for fp16/bf16 inputs with fp32 accumulation, and rounding the *output* to bf16 alone
+    costs 2^-9/sqrt(3) = 1.1e-3.  bf16 outputs get their own test with that floor added."""
     from graph_rws_b200 import core
     dev = torch.device("cuda")
     dtype = DT[dt]
+    if out_dtype is None:
+        out_dtype = torch.float32 if dt == "bf16" else dtype
     g = torch.Generator().manual_seed(seed)
     B = torch.randn(num_cols, N, generator=g).to(dtype)
     vals = torch.from_numpy(vals_np).to(dtype)
     C = core.spmm_raw(torch.from_numpy(wo).to(dev), torch.from_numpy(cols).to(dev), vals.to(dev), B.to(dev),
-                      algo=algo)
+                      out_dtype=out_dtype, algo=algo)
     torch.cuda.synchronize()
     C_ref = oracle.spmm_fwd(wo, cols, vals.float().numpy(), B.float().numpy())
     return C.float().cpu().numpy(), C_ref
@@ -47,6 +52,18 @@ def test_warp_mma_power_law_graph_with_split_windows(oracle, dt, N):
     assert (np.diff(wo) > 128).any(), "test graph must contain windows that get split"
     C, C_ref = _run(oracle, wo, cols, vals, g.num_nodes, N, dt, core.ALGO_WARP_MMA, seed=5)
     check_spmm_tolerance(C, C_ref, None, f"power-law N={N} {dt}")
+
+
+def test_bf16_output_rounding_floor(oracle):
+    """bf16 in, bf16 out: error = accumulation error (<= 1e-3) + one bf16 rounding of the result."""
+    from graph_rws_b200 import core
+    c = load_case(os.path.join(GOLDEN, "bcsr_chunglu_600.npz"))
+    C, C_ref = _run(oracle, c["window_offset"], c["cols"], c["vals"], 600, 128, "bf16", core.ALGO_WARP_MMA,
+                    out_dtype=torch.bfloat16)
+    fro = np.linalg.norm(C - C_ref) / np.linalg.norm(C_ref)
+    assert fro <= 1e-3 + 2.0 ** -9, fro
+    C16 = torch.from_numpy(C_ref).bfloat16().float().numpy()          # the checker's result rounded the same way
+    assert np.linalg.norm(C - C16) / np.linalg.norm(C16) <= 1e-3
 
 
 def test_padding_columns_contribute_nothing(oracle):
