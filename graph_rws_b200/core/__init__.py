@@ -8,8 +8,6 @@ The five reference names keep their argument meaning and return shapes:
 Unlike the reference, a missing native library is an ImportError here, never ``None``: there is
 no other implementation to fall back to.
 """
-import weakref
-
 import torch
 
 from . import _native
@@ -56,8 +54,10 @@ def _scratch(nbytes: int, device):
     return torch.empty(max(int(nbytes), 16), dtype=torch.uint8, device=device)
 
 
-def spmm_raw(window_offset, cols, vals, B, out_dtype=None, algo=None, num_tiles_bound=None):
-    """C[W*16, N] = A_bcsr @ B with values already in B's dtype and N % 8 == 0."""
+def spmm_raw(window_offset, cols, vals, B, out_dtype=None, algo=None, num_tiles_bound=None, check=False):
+    """C[W*16, N] = A_bcsr @ B with values already in B's dtype and N % 8 == 0.
+
+    ``check=True`` synchronises and raises if the tcgen05 kernel reported a timed-out wait."""
     lib = _native.lib()
     W = window_offset.shape[0] - 1
     K, N = B.shape
@@ -73,6 +73,10 @@ def spmm_raw(window_offset, cols, vals, B, out_dtype=None, algo=None, num_tiles_
         _ptr(window_offset), _ptr(cols), _ptr(vals), _DT[vals.dtype], _ptr(B), _DT[B.dtype], B.stride(0),
         C.data_ptr(), _DT[out_dtype], N, W, T, K, N, scratch.data_ptr(), scratch.numel(), algo,
         _stream(B.device)))
+    if check and lib.grws_spmm_resolve_algo(_DT[vals.dtype], N, algo) == ALGO_TCGEN05:
+        status = int(scratch[:4].view(torch.int32).item())
+        if status != 0:
+            raise RuntimeError(f"grws_b200 error -5: tcgen05 SpMM pipeline wait timed out (code {status})")
     return C
 
 

@@ -20,6 +20,7 @@ SIGNATURES = {
     "grws_last_error": (ctypes.c_char_p, []),
     "grws_version": (c_i32, []),
     "grws_spmm_scratch_bytes": (c_sz, [c_i64, c_i64, c_i64, c_i32]),
+    "grws_spmm_resolve_algo": (c_i32, [c_i32, c_i64, c_i32]),
     "grws_spmm_fwd": (c_i32, [c_vp, c_vp, c_vp, c_i32, c_vp, c_i32, c_i64, c_vp, c_i32, c_i64,
                               c_i64, c_i64, c_i64, c_i64, c_vp, c_sz, c_i32, c_vp]),
     "grws_csr_to_bcsr_scratch_bytes": (c_sz, [c_i64, c_i64]),

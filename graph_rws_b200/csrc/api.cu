@@ -42,6 +42,12 @@ size_t grws_spmm_scratch_bytes(int64_t num_windows, int64_t num_tiles_bound, int
 }
 
 __attribute__((visibility("default")))
+int grws_spmm_resolve_algo(int dtype, int64_t N, int algo) {
+    if (algo == GRWS_SPMM_AUTO) return spmm_tc5_supported(dtype, N) ? GRWS_SPMM_TCGEN05 : GRWS_SPMM_WARP_MMA;
+    return algo;
+}
+
+__attribute__((visibility("default")))
 int grws_spmm_fwd(const int64_t *window_offset, const int32_t *cols, const void *vals,
                   int val_dtype, const void *B, int b_dtype, int64_t ldb, void *C, int c_dtype,
                   int64_t ldc, int64_t num_windows, int64_t num_tiles_bound, int64_t K, int64_t N,

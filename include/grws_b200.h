@@ -69,6 +69,12 @@ int grws_version(void);
  * ------------------------------------------------------------------------------------------ */
 size_t grws_spmm_scratch_bytes(int64_t num_windows, int64_t num_tiles_bound, int64_t N, int algo);
 
+/* Which kernel `algo` resolves to for this dtype and width (GRWS_SPMM_WARP_MMA or _TCGEN05).
+ * The tcgen05 kernel keeps a status word (int32) in the first bytes of `scratch`: 0 after a
+ * clean run, otherwise the code of the wait that ran out (its waits on shared-memory barriers
+ * are bounded, so a broken pipeline ends with a status instead of hanging the GPU). */
+int grws_spmm_resolve_algo(int dtype, int64_t N, int algo);
+
 int grws_spmm_fwd(const int64_t *window_offset, const int32_t *cols, const void *vals,
                   int val_dtype, const void *B, int b_dtype, int64_t ldb, void *C, int c_dtype,
                   int64_t ldc, int64_t num_windows, int64_t num_tiles_bound, int64_t K, int64_t N,

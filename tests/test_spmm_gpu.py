@@ -24,7 +24,7 @@ def _run(oracle, wo, cols, vals_np, num_cols, N, dt, algo, seed=0, out_dtype=Non
     B = torch.randn(num_cols, N, generator=g).to(dtype)
     vals = torch.from_numpy(vals_np).to(dtype)
     C = core.spmm_raw(torch.from_numpy(wo).to(dev), torch.from_numpy(cols).to(dev), vals.to(dev), B.to(dev),
-                      out_dtype=out_dtype, algo=algo)
+                      out_dtype=out_dtype, algo=algo, check=True)
     torch.cuda.synchronize()
     C_ref = oracle.spmm_fwd(wo, cols, vals.float().numpy(), B.float().numpy())
     return C.float().cpu().numpy(), C_ref
@@ -52,6 +52,36 @@ def test_warp_mma_power_law_graph_with_split_windows(oracle, dt, N):
     assert (np.diff(wo) > 128).any(), "test graph must contain windows that get split"
     C, C_ref = _run(oracle, wo, cols, vals, g.num_nodes, N, dt, core.ALGO_WARP_MMA, seed=5)
     check_spmm_tolerance(C, C_ref, None, f"power-law N={N} {dt}")
+
+
+@pytest.mark.parametrize("dt,N", [("f16", 128), ("bf16", 128), ("f16", 256), ("bf16", 256)])
+@pytest.mark.parametrize("path", golden_cases(), ids=lambda p: os.path.basename(p)[5:-4])
+def test_tcgen05_matches_oracle_on_golden_graphs(oracle, path, dt, N):
+    from graph_rws_b200 import core
+    c = load_case(path)
+    num_cols = int(c["col_idx"].max()) + 1 if c["col_idx"].size else 8
+    C, C_ref = _run(oracle, c["window_offset"], c["cols"], c["vals"], num_cols, N, dt, core.ALGO_TCGEN05)
+    check_spmm_tolerance(C, C_ref, None, f"tcgen05 {os.path.basename(path)} N={N} {dt}")
+
+
+@pytest.mark.parametrize("dt,N,out", [("f16", 128, "f16"), ("bf16", 256, "f32"), ("f16", 256, "f32")])
+def test_tcgen05_power_law_graph(oracle, dt, N, out):
+    """Hub windows span several CTAs' tile ranges: exercises the partial tiles and the fix-up."""
+    from graph_rws_b200 import core
+    from graph_rws_b200.data import synthetic
+    g = synthetic.sym_normalized_csr(20000, *synthetic.chung_lu_edges(20000, 300000, 2.1, 23))
+    wo, cols, vals = oracle.csr_to_bcsr(g.num_nodes, g.row_ptr, g.col_idx, g.values)
+    assert np.diff(wo).max() > wo[-1] // 148 + 2, "a window must be longer than one CTA's share"
+    C, C_ref = _run(oracle, wo, cols, vals, g.num_nodes, N, dt, core.ALGO_TCGEN05, seed=5, out_dtype=DT[out])
+    check_spmm_tolerance(C, C_ref, None, f"tcgen05 power-law N={N} {dt}")
+
+
+def test_tcgen05_and_warp_paths_agree(oracle):
+    from graph_rws_b200 import core
+    c = load_case(os.path.join(GOLDEN, "bcsr_chunglu_600.npz"))
+    a, _ = _run(oracle, c["window_offset"], c["cols"], c["vals"], 600, 128, "f16", core.ALGO_TCGEN05, out_dtype=torch.float32)
+    b, _ = _run(oracle, c["window_offset"], c["cols"], c["vals"], 600, 128, "f16", core.ALGO_WARP_MMA, out_dtype=torch.float32)
+    np.testing.assert_allclose(a, b, rtol=1e-5, atol=1e-5)
 
 
 def test_bf16_output_rounding_floor(oracle):
