@@ -221,13 +221,9 @@ def spmm_transpose(window_offset, original_col_indices, values_condensed, grad_o
     return out[:num_cols]
 
 
-def reindex_bcsr(col_indices, values_condensed, active_windows, tile_rows=16, tile_cols=8):
-    raise NotImplementedError("reindex_bcsr lands with the sampler kernels")
-
-
-def sample_all_layers(*args, **kwargs):
-    raise NotImplementedError("sample_all_layers lands with the sampler kernels")
-
+from .sampling import (SamplingTimingResult, bcsr_to_csr, build_block, reindex_bcsr,  # noqa: E402,F401
+                       sample_all_layers, sample_hop, sample_layers_csr)
 
 __all__ = ["sample_all_layers", "spmm_tc", "spmm_transpose", "csr_to_bcsr_cpu", "reindex_bcsr",
-           "csr_to_bcsr", "bcsr_transpose", "spmm_raw", "set_spmm_timing", "set_spmm_algo"]
+           "csr_to_bcsr", "bcsr_transpose", "spmm_raw", "set_spmm_timing", "set_spmm_algo",
+           "bcsr_to_csr", "sample_hop", "build_block", "sample_layers_csr", "SamplingTimingResult"]

@@ -30,6 +30,15 @@ SIGNATURES = {
     "grws_bcsr_transpose_count": (c_i32, [c_vp, c_vp, c_vp, c_i32, c_i64, c_i64, c_vp, c_vp, c_sz, c_vp]),
     "grws_bcsr_transpose_fill": (c_i32, [c_vp, c_vp, c_vp, c_i32, c_i64, c_i64, c_vp, c_vp, c_vp,
                                          c_vp, c_sz, c_vp]),
+    "grws_bcsr_to_csr_scratch_bytes": (c_sz, [c_i64]),
+    "grws_bcsr_to_csr_count": (c_i32, [c_vp, c_vp, c_vp, c_i32, c_i64, c_i64, c_vp, c_vp, c_sz, c_vp]),
+    "grws_bcsr_to_csr_fill": (c_i32, [c_vp, c_vp, c_vp, c_i32, c_i64, c_i64, c_vp, c_vp, c_vp, c_vp]),
+    "grws_sample_hop": (c_i32, [c_vp, c_vp, c_vp, c_vp, c_i64, c_i32, ctypes.c_uint64, ctypes.c_uint32,
+                                c_vp, c_vp, c_vp, c_vp]),
+    "grws_dedup_scratch_bytes": (c_sz, [c_i64, c_i32]),
+    "grws_dedup_reindex": (c_i32, [c_vp, c_i64, c_vp, c_i32, c_vp, c_vp, c_vp, c_vp, c_vp, c_sz, c_vp]),
+    "grws_block_compact": (c_i32, [c_vp, c_vp, c_i64, c_i32, c_vp, c_vp, c_vp, c_vp]),
+    "grws_reindex_bcsr": (c_i32, [c_vp, c_vp, c_i32, c_vp, c_i64, c_i64, c_i32, c_i32, c_vp, c_vp]),
 }
 
 _lib = None

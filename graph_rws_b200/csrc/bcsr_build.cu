@@ -166,6 +166,33 @@ __global__ void transpose_entries_kernel(int64_t W, const int64_t *__restrict__ 
     }
 }
 
+// BCSR -> CSR (not transposed): one warp per window, lane r < 16 walks row r of every tile in
+// order.  Column ids are ascending inside a window, so every CSR row comes out ascending.
+// MODE 0 counts the non-zero entries of each row, MODE 1 writes them.
+template <typename T, int MODE>
+__global__ void bcsr_rows_kernel(int64_t W, int64_t num_rows, const int64_t *__restrict__ window_offset,
+                                 const int32_t *__restrict__ cols, const T *__restrict__ vals,
+                                 int64_t *__restrict__ row_ptr, int32_t *__restrict__ out_col,
+                                 float *__restrict__ out_val) {
+    const int64_t w = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int r = threadIdx.x & 31;
+    if (w >= W || r >= TILE_ROWS) return;
+    const int64_t row = w * TILE_ROWS + r;
+    if (row >= num_rows) return;
+    int64_t o = (MODE == 1) ? row_ptr[row] : 0;
+    for (int64_t t = window_offset[w]; t < window_offset[w + 1]; ++t) {
+#pragma unroll
+        for (int c = 0; c < TILE_COLS; ++c) {
+            const int32_t col = cols[t * TILE_COLS + c];
+            const float v = to_float<T>(vals[t * TILE_ELEMS + r * TILE_COLS + c]);
+            if (col < 0 || v == 0.0f) continue;
+            if (MODE == 1) { out_col[o] = col; out_val[o] = v; }
+            ++o;
+        }
+    }
+    if (MODE == 0) row_ptr[row + 1] = o;
+}
+
 }  // namespace grws
 
 using namespace grws;
@@ -304,6 +331,55 @@ int grws_bcsr_transpose_fill(const int64_t *window_offset, const int32_t *cols, 
         transpose_entries_kernel<__nv_bfloat16, 1><<<W, 128, 0, st>>>(num_windows, window_offset, cols, (const __nv_bfloat16 *)vals, num_cols, cursor, out_col, out_val);
     else
         return fail(GRWS_ERR_UNSUPPORTED, "bad value dtype %d", val_dtype);
+    GRWS_CUDA_TRY(cudaGetLastError());
+    return GRWS_OK;
+}
+
+// BCSR -> CSR of the same matrix, two phases like the other builders.
+__attribute__((visibility("default")))
+size_t grws_bcsr_to_csr_scratch_bytes(int64_t num_rows) {
+    size_t s3 = 0;
+    cub::DeviceScan::InclusiveSum(nullptr, s3, (const int64_t *)nullptr, (int64_t *)nullptr, (int)(num_rows + 1));
+    return align_up(s3);
+}
+
+__attribute__((visibility("default")))
+int grws_bcsr_to_csr_count(const int64_t *window_offset, const int32_t *cols, const void *vals, int val_dtype,
+                           int64_t num_windows, int64_t num_rows, int64_t *row_ptr, void *scratch,
+                           size_t scratch_bytes, void *stream) {
+    GRWS_REQUIRE(num_windows >= 0 && num_rows >= 0 && num_rows <= num_windows * TILE_ROWS, "bad size");
+    GRWS_REQUIRE(num_rows < 0x7fffffffLL, "size beyond 2^31");
+    GRWS_REQUIRE(window_offset && row_ptr && scratch, "null pointer");
+    if (scratch_bytes < grws_bcsr_to_csr_scratch_bytes(num_rows)) return fail(GRWS_ERR_SCRATCH, "bcsr_to_csr scratch too small");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    GRWS_CUDA_TRY(cudaMemsetAsync(row_ptr, 0, (size_t)(num_rows + 1) * 8, st));
+    if (num_windows > 0) {
+        const unsigned nb = blocks_for(num_windows * 32, 256);
+        if (val_dtype == GRWS_F32) bcsr_rows_kernel<float, 0><<<nb, 256, 0, st>>>(num_windows, num_rows, window_offset, cols, (const float *)vals, row_ptr, nullptr, nullptr);
+        else if (val_dtype == GRWS_F16) bcsr_rows_kernel<__half, 0><<<nb, 256, 0, st>>>(num_windows, num_rows, window_offset, cols, (const __half *)vals, row_ptr, nullptr, nullptr);
+        else if (val_dtype == GRWS_BF16) bcsr_rows_kernel<__nv_bfloat16, 0><<<nb, 256, 0, st>>>(num_windows, num_rows, window_offset, cols, (const __nv_bfloat16 *)vals, row_ptr, nullptr, nullptr);
+        else return fail(GRWS_ERR_UNSUPPORTED, "bad value dtype %d", val_dtype);
+    }
+    size_t tmp = scratch_bytes;
+    GRWS_CUDA_TRY(cub::DeviceScan::InclusiveSum(scratch, tmp, row_ptr, row_ptr, (int)(num_rows + 1), st));
+    GRWS_CUDA_TRY(cudaGetLastError());
+    return GRWS_OK;
+}
+
+__attribute__((visibility("default")))
+int grws_bcsr_to_csr_fill(const int64_t *window_offset, const int32_t *cols, const void *vals, int val_dtype,
+                          int64_t num_windows, int64_t num_rows, const int64_t *row_ptr, int32_t *out_col,
+                          float *out_val, void *stream) {
+    GRWS_REQUIRE(num_windows >= 0 && num_rows >= 0, "bad size");
+    if (num_windows == 0) return GRWS_OK;
+    GRWS_REQUIRE(window_offset && row_ptr, "null pointer");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int64_t *rp = const_cast<int64_t *>(row_ptr);
+    const unsigned nb = blocks_for(num_windows * 32, 256);
+    if (val_dtype == GRWS_F32) bcsr_rows_kernel<float, 1><<<nb, 256, 0, st>>>(num_windows, num_rows, window_offset, cols, (const float *)vals, rp, out_col, out_val);
+    else if (val_dtype == GRWS_F16) bcsr_rows_kernel<__half, 1><<<nb, 256, 0, st>>>(num_windows, num_rows, window_offset, cols, (const __half *)vals, rp, out_col, out_val);
+    else if (val_dtype == GRWS_BF16) bcsr_rows_kernel<__nv_bfloat16, 1><<<nb, 256, 0, st>>>(num_windows, num_rows, window_offset, cols, (const __nv_bfloat16 *)vals, rp, out_col, out_val);
+    else return fail(GRWS_ERR_UNSUPPORTED, "bad value dtype %d", val_dtype);
     GRWS_CUDA_TRY(cudaGetLastError());
     return GRWS_OK;
 }

@@ -9,9 +9,10 @@
 //   * the B operand of the instruction is the raw pair of BCSR tiles: an fp16 [16][8] tile is two
 //     8x16-byte core matrices, consecutive tiles are 256 bytes apart, so the tiles are streamed
 //     from HBM by TMA bulk copies (cp.async.bulk) straight into a K-major, no-swizzle operand;
-//   * the A operand is the gathered rows of the dense matrix, MN-major: each 16-byte piece of a
-//     gathered row is written to its core-matrix slot by cp.async (L2 -> shared memory, no
-//     registers), rows whose column id is -1 are zero-filled;
+//   * the A operand is the gathered rows of the dense matrix, MN-major with the 128-byte swizzle:
+//     a gathered row is two 128-byte lines, fetched from L2 by the TMA unit in gather mode
+//     (cp.async.bulk.tensor ... tile::gather4: four rows by 64 features per copy, no registers, no
+//     per-thread address arithmetic); a column id of -1 is out of bounds and reads zeros;
 //   * accumulators live in tensor memory (16 fp32 columns per slab), four deep, so the epilogue
 //     of one window overlaps the MMAs of the next.
 //
@@ -19,9 +20,10 @@
 // so power-law window lengths do not matter); a window cut by a range boundary is finished by the
 // fix-up kernel from fp32 partial tiles in scratch, in a fixed order.
 //
-// Warp roles: 0-3 gather producers, 4-7 epilogue (TMEM -> registers -> global), 8 MMA issuer,
-// 9 TMA producer for tile values and column ids.  Every mbarrier wait is bounded: on time-out the
+// Warp roles: 0-7 gather producers (two per pipeline stage), 8-11 epilogue (TMEM -> registers ->
+// global), 12 MMA issuer, 13 TMA producer for tile values and column ids.  Every mbarrier wait is bounded: on time-out the
 // kernel raises the status word at the start of scratch and all roles drain and return.
+#include <cuda.h>      // CUtensorMap and the cuTensorMapEncodeTiled prototype (resolved at run time)
 #include <stdlib.h>
 
 #include "grws_common.cuh"
@@ -35,19 +37,31 @@ constexpr int STAGE_SLOTS = STAGE_TILES * TILE_COLS; // gathered rows per stage
 constexpr int MMAS_PER_STAGE = STAGE_TILES / 2;
 constexpr int SLAB = 128;                            // features per MMA (its M dimension)
 constexpr int CHUNKS = SLAB * 2 / 16;                // 16-byte pieces of a 128-feature row
-constexpr int A_SBO = 272;                           // bytes between 8-feature core-matrix columns (odd
-                                                     // multiple of 16: conflict-free cp.async writes)
-constexpr int A_LBO = 128;                           // bytes between the two 8-slot halves of a K-step
-constexpr int A_MMA_BYTES = CHUNKS * A_SBO;          // one K-step of one slab
+// A operand of one K-step (16 slots x 128 features), MN-major with the 128-byte swizzle: four
+// 1024-byte atoms [slot half][feature half], an atom holds 8 slots x 64 features, slot k at
+// k * 128 bytes, its 16-byte piece c stored at piece c ^ k.  A gathered row therefore lands as
+// two contiguous (permuted) 128-byte lines, which cp.async moves as whole lines.
+constexpr int A_ATOM_BYTES = 1024;
+constexpr int A_LBO = A_ATOM_BYTES;                  // between the two 64-feature halves
+constexpr int A_SBO = 2 * A_ATOM_BYTES;              // between the two 8-slot halves
+constexpr int A_MMA_BYTES = 4 * A_ATOM_BYTES;        // one K-step of one slab
 constexpr int TILE_BYTES = TILE_ELEMS * 2;           // 256
 constexpr int META_TILE_BYTES = STAGE_TILES * TILE_BYTES;
 constexpr int META_COL_BYTES = STAGE_TILES * TILE_COLS * 4;
-constexpr int META_BYTES = META_TILE_BYTES + META_COL_BYTES;
+constexpr int META_CMD_BYTES = 16;                   // per-stage command word written by the TMA warp
+constexpr int META_BYTES = META_TILE_BYTES + META_COL_BYTES + META_CMD_BYTES;
+// command word: bits 0-3 tile count, bit 4 first stage of a window segment, bit 5 last stage,
+// bit 6 end of this CTA's work
+constexpr uint32_t CMD_FIRST = 1u << 4, CMD_LAST = 1u << 5, CMD_END = 1u << 6;
 constexpr int NACC = 4;                              // accumulator buffers in tensor memory
-constexpr int NUM_PRODUCERS = 128;
+constexpr int NUM_PRODUCER_WARPS = 8;                 // two per gather slot
 constexpr int NUM_EPILOGUE = 128;
-constexpr int NUM_THREADS = 320;
-constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;    // a wait gives up after two seconds
+constexpr int EPILOGUE_WARP0 = NUM_PRODUCER_WARPS;       // four warps; warp % 4 is its TMEM lane quarter
+constexpr int MMA_WARP = EPILOGUE_WARP0 + 4;
+constexpr int TMA_WARP = MMA_WARP + 1;
+constexpr int NUM_THREADS = (TMA_WARP + 1) * 32;
+static_assert(EPILOGUE_WARP0 % 4 == 0, "epilogue warps must start at a multiple of four");
+constexpr long long WAIT_LIMIT_CYCLES = 3000000000ll; // a wait gives up after about 1.5-2.5 s of SM clocks
 
 enum : int { ST_OK = 0, ST_TIMEOUT_FULL = 1, ST_TIMEOUT_EMPTY = 2, ST_TIMEOUT_ACC = 3, ST_TIMEOUT_META = 4 };
 
@@ -59,9 +73,12 @@ struct Params {
     void *C;
     float *partial;
     int *status;
+    int64_t *fix;     // [grid][4]: range start, window whose first piece this CTA holds (-1: none), its end, unused
     int64_t W, N, ldb, ldc;
     int c_dtype;
     int is_bf16;
+    int skip;         // experiment knob (GRWS_TC5_SKIP): 1 = issue no MMAs, 2 = gather nothing, 4 = no output stores
+    long long *dbg;   // optional [grid][16] cycle counters (wait time per role), null when not profiling
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -84,22 +101,39 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
                  : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok;
 }
-__device__ __forceinline__ uint64_t global_ns() {
-    uint64_t t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return t;
-}
-// bounded wait: gives up after WAIT_LIMIT_NS or when another role already aborted
+// bounded wait: gives up after WAIT_LIMIT_CYCLES SM clocks or when another role already aborted.
+// (The SM clock is used because reading %globaltimer costs about a microsecond per read.)
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
     if (mbar_try_wait(bar, parity)) return true;
-    const uint64_t t0 = global_ns();
+    long long t0 = 0;
     for (uint32_t i = 0;; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 31u) == 31u) {
+        if ((i & 63u) == 63u) {
             if (*abort_flag) return false;
-            if (global_ns() - t0 > WAIT_LIMIT_NS) return false;
+            const long long now = clock64();
+            if (t0 == 0) t0 = now;
+            if (now - t0 > WAIT_LIMIT_CYCLES) return false;
         }
     }
+}
+// wait that adds its duration to `acc` in the profiling build of the kernel
+template <bool PROF>
+__device__ __forceinline__ bool mbar_wait_t(uint32_t bar, uint32_t parity, volatile int *abort_flag, long long &acc) {
+    if constexpr (PROF) {
+        const long long t0 = clock64();
+        const bool ok = mbar_wait(bar, parity, abort_flag);
+        acc += clock64() - t0;
+        return ok;
+    } else {
+        return mbar_wait(bar, parity, abort_flag);
+    }
+}
+// timeline of the first stages of CTA 0 (profiling build): event e of stage `it`
+template <bool PROF> __device__ __forceinline__ void prof_mark(long long *dbg, uint32_t it, int e) {
+    if constexpr (PROF) { if (dbg && blockIdx.x == 0 && it < 64) dbg[6144 + it * 8 + e] = clock64(); }
+}
+template <bool PROF> __device__ __forceinline__ long long prof_clock() {
+    if constexpr (PROF) return clock64(); else return 0;
 }
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, uint32_t src_bytes, uint64_t pol) {
     asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2, %3;"
@@ -112,6 +146,15 @@ __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wai
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar, uint64_t pol) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
                  ::"r"(dst), "l"(src), "r"(bytes), "r"(bar), "l"(pol) : "memory");
+}
+// TMA gather of four rows of the dense operand (tile::gather4): 64 features of rows r0..r3 land as
+// four consecutive 128-byte lines, already permuted for the 128-byte-swizzle operand layout.  A
+// negative or too large row id is out of bounds and reads zeros.
+__device__ __forceinline__ void tma_gather4(uint32_t dst, const CUtensorMap *map, uint32_t bar, int x, int r0, int r1,
+                                            int r2, int r3, uint64_t pol) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes.L2::cache_hint"
+                 " [%0], [%1, {%3, %4, %5, %6, %7}], [%2], %8;"
+                 ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(r0), "r"(r1), "r"(r2), "r"(r3), "l"(pol) : "memory");
 }
 __device__ __forceinline__ uint64_t policy_keep() {
     uint64_t p;
@@ -152,10 +195,10 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
-// shared-memory matrix descriptor, no swizzle (layout type 0), descriptor version 1
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+// shared-memory matrix descriptor (version 1); layout 0 = no swizzle, 2 = 128-byte swizzle
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout) {
     return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo_bytes >> 4) << 16) |
-           ((uint64_t)(sbo_bytes >> 4) << 32) | (1ull << 46);
+           ((uint64_t)(sbo_bytes >> 4) << 32) | (1ull << 46) | ((uint64_t)layout << 61);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -213,13 +256,17 @@ struct SharedStorage {
 };
 
 template <int NH> struct Cfg {
-    // shared-memory budget: one CTA per SM
-    static constexpr int kStages = (NH == 1) ? 8 : 4;
-    static constexpr int kMeta = 2 * kStages;
+    // two CTAs per SM for one slab (their MMA-issuing threads overlap each other's latency),
+    // one CTA per SM for two slabs (a stage is twice as large)
+    static constexpr int kCtasPerSm = (NH == 1) ? 2 : 1;
+    static constexpr int kStages = 4;
+    // tile / column-id slots: the TMA warp runs kMeta - kStages stages ahead of the data it has
+    // already landed, which has to cover the HBM latency of the tile stream
+    static constexpr int kMeta = (NH == 1) ? 16 : 20;
     static constexpr int kStageBytes = MMAS_PER_STAGE * NH * A_MMA_BYTES;
     static constexpr int kAccCols = 16 * NH;
     static constexpr int kTmemCols = (NACC * kAccCols) < 32 ? 32 : NACC * kAccCols;   // 64 or 128: powers of two
-    static constexpr size_t kSmem = 1024 + sizeof(SharedStorage) + (size_t)kStages * kStageBytes + (size_t)kMeta * META_BYTES;
+    static constexpr size_t kSmem = 1024 + sizeof(SharedStorage) + 16 + (size_t)kStages * kStageBytes + (size_t)kMeta * META_BYTES;
 };
 
 __device__ __forceinline__ void raise(Params const &prm, SharedStorage *ss, int code) {
@@ -227,33 +274,27 @@ __device__ __forceinline__ void raise(Params const &prm, SharedStorage *ss, int 
     atomicMax(prm.status, code);
 }
 
-template <int NH>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
-spmm_tc5_kernel(const Params prm) {
+template <int NH, bool PROF>
+__global__ void __launch_bounds__(NUM_THREADS, Cfg<NH>::kCtasPerSm)
+spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
     using C = Cfg<NH>;
     extern __shared__ uint8_t smem_raw[];
-    // 1024-byte alignment is not required by the no-swizzle layouts; 128 is kept for the bulk copies
-    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
-    SharedStorage *ss = reinterpret_cast<SharedStorage *>(smem);
-    uint8_t *ring_g = smem + ((sizeof(SharedStorage) + 127) & ~size_t(127));
+    // the swizzled operand atoms must start on 1024-byte boundaries
+    uint8_t *ring_g = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t *ring_m = ring_g + (size_t)C::kStages * C::kStageBytes;
+    SharedStorage *ss = reinterpret_cast<SharedStorage *>(ring_m + (size_t)C::kMeta * META_BYTES);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t W = prm.W;
-    const int64_t T = __ldg(prm.window_offset + W);
-    const int64_t G = gridDim.x;
-    int64_t chunk = (T + G - 1) / G;
-    chunk = (chunk + 1) & ~int64_t(1);
-    if (chunk < 2) chunk = 2;
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < C::kStages; ++i) { mbar_init(smem_u32(&ss->full_g[i]), NUM_PRODUCERS); mbar_init(smem_u32(&ss->empty_g[i]), 1); }
+        for (int i = 0; i < C::kStages; ++i) { mbar_init(smem_u32(&ss->full_g[i]), 1); mbar_init(smem_u32(&ss->empty_g[i]), 1); }
         for (int i = 0; i < C::kMeta; ++i) { mbar_init(smem_u32(&ss->full_m[i]), 1); mbar_init(smem_u32(&ss->empty_m[i]), 1); }
         for (int i = 0; i < NACC; ++i) { mbar_init(smem_u32(&ss->acc_full[i]), 1); mbar_init(smem_u32(&ss->acc_empty[i]), NUM_EPILOGUE); }
         ss->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 8) {
+    if (warp == MMA_WARP) {
         tmem_alloc(smem_u32(&ss->tmem_base), C::kTmemCols);
         tmem_relinquish();
     }
@@ -263,227 +304,293 @@ spmm_tc5_kernel(const Params prm) {
     const uint32_t tmem_base = ss->tmem_base;
     volatile int *abort_flag = &ss->abort_flag;
 
-    // this CTA's tile range (no cut is moved: long_window = 0 splits any window a cut falls into)
-    int64_t w_first, w_unused;
-    const int64_t s = warp_cut(prm.window_offset, W, T, blockIdx.x, G, chunk, 0, lane, &w_first);
-    const int64_t e = warp_cut(prm.window_offset, W, T, (int64_t)blockIdx.x + 1, G, chunk, 0, lane, &w_unused);
-    Walker wk;
-    wk.init(prm.window_offset, W, s, e, blockIdx.x == 0 ? 0 : w_first, lane);
+    if (warp == TMA_WARP || warp >= EPILOGUE_WARP0 && warp < MMA_WARP) {
+        // ---- the two roles that walk the window structure: this CTA's tile range [s, e)
+        const int64_t T = __ldg(prm.window_offset + W);
+        const int64_t G = gridDim.x;
+        int64_t chunk = (T + G - 1) / G;
+        chunk = (chunk + 1) & ~int64_t(1);
+        if (chunk < 2) chunk = 2;
+        // a cut inside a window of at most chunk/16 tiles moves back to that window's start, so
+        // only long windows are ever split between CTAs (tile counts stay balanced within 1/16)
+        const int64_t long_window = chunk >> 4;
+        int64_t w_first, w_unused;
+        const int64_t s = warp_cut(prm.window_offset, W, T, blockIdx.x, G, chunk, long_window, lane, &w_first);
+        const int64_t e = warp_cut(prm.window_offset, W, T, (int64_t)blockIdx.x + 1, G, chunk, long_window, lane, &w_unused);
+        Walker wk;
+        wk.init(prm.window_offset, W, s, e, blockIdx.x == 0 ? 0 : w_first, lane);
 
-    if (warp == 9) {
-        // ------------------------------------------------------------------ TMA producer
-        const uint64_t pol = policy_stream();
-        uint32_t it = 0;
-        bool ok = true;
-        while (ok && wk.next_segment(lane)) {
-            for (int64_t t0 = wk.seg_s; ok && t0 < wk.seg_e; t0 += STAGE_TILES, ++it) {
-                const uint32_t slot = it % C::kMeta, ph = (it / C::kMeta) & 1u;
-                const int ntiles = (int)min((int64_t)STAGE_TILES, wk.seg_e - t0);
-                if (lane == 0) {
-                    ok = mbar_wait(smem_u32(&ss->empty_m[slot]), ph ^ 1u, abort_flag);
+        if (warp == TMA_WARP) {
+            // -------------------------------------------------------------- TMA producer
+            // streams tile values and column ids of every stage and tells the other roles, through
+            // the command word of the stage, what the stage holds
+            const uint64_t pol = policy_stream();
+            uint32_t it = 0;
+            bool ok = true;
+            long long w_empty_m = 0;
+            const long long t_start = prof_clock<PROF>();
+            while (ok && wk.next_segment(lane)) {
+                for (int64_t t0 = wk.seg_s; ok && t0 < wk.seg_e; t0 += STAGE_TILES, ++it) {
+                    const uint32_t slot = it % C::kMeta, ph = (it / C::kMeta) & 1u;
+                    const int ntiles = (int)min((int64_t)STAGE_TILES, wk.seg_e - t0);
+                    if (lane == 0) ok = mbar_wait_t<PROF>(smem_u32(&ss->empty_m[slot]), ph ^ 1u, abort_flag, w_empty_m);
+                    ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+                    if (ok && (ntiles & 1)) {
+                        // an odd tile count leaves the second tile of the last K-step without data:
+                        // zero it (the MMA multiplies it with zero rows, which must not meet NaNs)
+                        if (lane < 16)
+                            *reinterpret_cast<uint4 *>(ring_m + (size_t)slot * META_BYTES + (size_t)ntiles * TILE_BYTES + lane * 16) = make_uint4(0u, 0u, 0u, 0u);
+                        fence_async_smem();
+                        __syncwarp();
+                    }
+                    if (lane == 0) {
+                        if (ok) {
+                            const uint32_t bar = smem_u32(&ss->full_m[slot]);
+                            uint8_t *dst = ring_m + (size_t)slot * META_BYTES;
+                            *reinterpret_cast<volatile uint32_t *>(dst + META_TILE_BYTES + META_COL_BYTES) =
+                                (uint32_t)ntiles | (t0 == wk.seg_s ? CMD_FIRST : 0u) | (t0 + STAGE_TILES >= wk.seg_e ? CMD_LAST : 0u);
+                            if (prm.skip & 8) {
+                                mbar_arrive(bar);
+                            } else {
+                            mbar_expect_tx(bar, (uint32_t)ntiles * (TILE_BYTES + TILE_COLS * 4));   // release: publishes the command
+                            bulk_g2s(smem_u32(dst), static_cast<const uint8_t *>(prm.vals) + t0 * TILE_BYTES,
+                                     (uint32_t)ntiles * TILE_BYTES, bar, pol);
+                            bulk_g2s(smem_u32(dst + META_TILE_BYTES), prm.cols + t0 * TILE_COLS,
+                                     (uint32_t)ntiles * TILE_COLS * 4, bar, pol);
+                            }
+                            prof_mark<PROF>(prm.dbg, it, 0);
+                        } else {
+                            raise(prm, ss, ST_TIMEOUT_META);
+                        }
+                    }
+                    ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+                }
+            }
+            if (lane == 0) {                // one end marker per producer warp; the MMA warp stops at the first
+                for (int j = 0; ok && j < C::kStages; ++j, ++it) {
+                    const uint32_t slot = it % C::kMeta, ph = (it / C::kMeta) & 1u;
+                    ok = mbar_wait_t<PROF>(smem_u32(&ss->empty_m[slot]), ph ^ 1u, abort_flag, w_empty_m);
                     if (ok) {
-                        const uint32_t bar = smem_u32(&ss->full_m[slot]);
-                        uint8_t *dst = ring_m + (size_t)slot * META_BYTES;
-                        mbar_expect_tx(bar, (uint32_t)ntiles * (TILE_BYTES + TILE_COLS * 4));
-                        bulk_g2s(smem_u32(dst), static_cast<const uint8_t *>(prm.vals) + t0 * TILE_BYTES,
-                                 (uint32_t)ntiles * TILE_BYTES, bar, pol);
-                        bulk_g2s(smem_u32(dst + META_TILE_BYTES), prm.cols + t0 * TILE_COLS,
-                                 (uint32_t)ntiles * TILE_COLS * 4, bar, pol);
+                        *reinterpret_cast<volatile uint32_t *>(ring_m + (size_t)slot * META_BYTES + META_TILE_BYTES + META_COL_BYTES) = CMD_END;
+                        mbar_arrive(smem_u32(&ss->full_m[slot]));
                     } else {
                         raise(prm, ss, ST_TIMEOUT_META);
                     }
                 }
-                ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
             }
-        }
-    } else if (warp < 4) {
-        // ------------------------------------------------------------------ gather producers
-        const uint64_t keep = policy_keep();
-        const int p = threadIdx.x;                 // 0..127
-        const int prow = p >> 4, pchunk = p & 15;  // row inside a group of 8, 16-byte piece of the slab
-        const char *Bb = static_cast<const char *>(prm.B);
-        uint32_t it = 0;
-        bool ok = true;
-        while (ok && wk.next_segment(lane)) {
-            for (int64_t t0 = wk.seg_s; ok && t0 < wk.seg_e; t0 += STAGE_TILES, ++it) {
-                const uint32_t gs = it % C::kStages, gph = (it / C::kStages) & 1u;
-                const uint32_t ms = it % C::kMeta, mph = (it / C::kMeta) & 1u;
-                const int ntiles = (int)min((int64_t)STAGE_TILES, wk.seg_e - t0);
-                const int nrows = ((ntiles + 1) >> 1) * 16;        // rows the MMAs of this stage read
-                // column ids have landed; the gather slot has been released by the MMA warp
-                ok = mbar_wait(smem_u32(&ss->full_m[ms]), mph, abort_flag);
-                if (ok) ok = mbar_wait(smem_u32(&ss->empty_g[gs]), gph ^ 1u, abort_flag);
-                ok = __all_sync(0xffffffffu, ok) != 0;          // keep the warp together
-                if (!ok) { raise(prm, ss, ST_TIMEOUT_EMPTY); break; }
-                const int32_t *scol = reinterpret_cast<const int32_t *>(ring_m + (size_t)ms * META_BYTES + META_TILE_BYTES);
-                const uint32_t stage_base = smem_u32(ring_g + (size_t)gs * C::kStageBytes);
+            if (PROF && prm.dbg && lane == 0) { prm.dbg[blockIdx.x * 16 + 0] = w_empty_m; prm.dbg[blockIdx.x * 16 + 1] = prof_clock<PROF>() - t_start; }
+        } else {
+            // -------------------------------------------------------------- epilogue warps
+            const uint64_t pol = policy_stream();
+            const int q = warp & 3;                        // TMEM lane quarter this warp may read
+            uint32_t ai = 0;
+            bool ok = true;
+            long long w_af = 0;
+            int64_t tail_w = -1, tail_b = 0;
+            while (ok && wk.next_segment(lane)) {
+                const int64_t w = wk.window();
+                if (wk.tail()) { tail_w = w; tail_b = wk.b; }
+                const bool nonempty = wk.seg_e > wk.seg_s;
+                uint32_t v[NH][16];
+                if (nonempty) {
+                    const uint32_t buf = ai % NACC, aph = (ai / NACC) & 1u;
+                    ++ai;
+                    ok = mbar_wait_t<PROF>(smem_u32(&ss->acc_full[buf]), aph, abort_flag, w_af);
+                    ok = __all_sync(0xffffffffu, ok) != 0;
+                    if (!ok) { raise(prm, ss, ST_TIMEOUT_ACC); break; }
+                    tc_fence_after();
 #pragma unroll
-                for (int j = 0; j < STAGE_SLOTS / 8; ++j) {
-                    const int row = 8 * j + prow;
-                    if (row < nrows) {
-                        const int32_t col = (row < ntiles * TILE_COLS) ? scol[row] : -1;
-                        const int m = row >> 4, slot16 = row & 15;
-                        const char *src = Bb + ((int64_t)(col >= 0 ? col : 0) * prm.ldb) * 2 + pchunk * 16;
-                        const uint32_t nbytes = col >= 0 ? 16u : 0u;
+                    for (int h = 0; h < NH; ++h)
+                        tmem_ld16(tmem_base + ((uint32_t)(32 * q) << 16) + buf * C::kAccCols + h * 16, v[h]);
+                    tmem_ld_wait();
+                    tc_fence_before();
+                    mbar_arrive(smem_u32(&ss->acc_empty[buf]));
+                } else {
 #pragma unroll
-                        for (int h = 0; h < NH; ++h) {
-                            const uint32_t dst = stage_base + (uint32_t)((m * NH + h) * A_MMA_BYTES + pchunk * A_SBO +
-                                                                         (slot16 >> 3) * A_LBO + (slot16 & 7) * 16);
-                            cp_async16(dst, src + h * (SLAB * 2), nbytes, keep);
-                        }
-                    }
+                    for (int h = 0; h < NH; ++h)
+#pragma unroll
+                        for (int r = 0; r < 16; ++r) v[h][r] = 0u;
                 }
-                // an odd tile count leaves the second tile of the last K-step unwritten: zero it
-                if ((ntiles & 1) && p < 16) {
-                    const uint32_t dst = smem_u32(ring_m + (size_t)ms * META_BYTES + (size_t)ntiles * TILE_BYTES) + p * 16;
-                    cp_async16(dst, Bb, 0u, keep);
-                }
-                cp_async_arrive_noinc(smem_u32(&ss->full_g[gs]));
-            }
-        }
-        cp_async_wait_all();
-    } else if (warp == 8) {
-        // ------------------------------------------------------------------ MMA issuer
-        const uint32_t idesc = (1u << 4) | ((uint32_t)prm.is_bf16 << 7) | ((uint32_t)prm.is_bf16 << 10) |
-                               (1u << 15) | ((16u >> 3) << 17) | ((128u >> 4) << 24);
-        uint32_t it = 0, ai = 0;
-        bool ok = true;
-        while (ok && wk.next_segment(lane)) {
-            if (wk.seg_e <= wk.seg_s) continue;            // empty window: the epilogue writes zeros
-            const uint32_t buf = ai % NACC, aph = (ai / NACC) & 1u;
-            ++ai;
-            if (lane == 0) {
-                ok = mbar_wait(smem_u32(&ss->acc_empty[buf]), aph ^ 1u, abort_flag);
-                if (!ok) raise(prm, ss, ST_TIMEOUT_ACC);
-            }
-            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-            for (int64_t t0 = wk.seg_s; ok && t0 < wk.seg_e; t0 += STAGE_TILES, ++it) {
-                const uint32_t gs = it % C::kStages, gph = (it / C::kStages) & 1u;
-                const uint32_t ms = it % C::kMeta, mph = (it / C::kMeta) & 1u;
-                const int ntiles = (int)min((int64_t)STAGE_TILES, wk.seg_e - t0);
-                const int nmma = (ntiles + 1) >> 1;
-                if (lane == 0) {
-                    ok = mbar_wait(smem_u32(&ss->full_m[ms]), mph, abort_flag);
-                    if (ok) ok = mbar_wait(smem_u32(&ss->full_g[gs]), gph, abort_flag);
-                    if (ok) {
-                        fence_async_smem();
-                        tc_fence_after();
-                        const uint32_t a_base = smem_u32(ring_g + (size_t)gs * C::kStageBytes);
-                        const uint32_t b_base = smem_u32(ring_m + (size_t)ms * META_BYTES);
-                        for (int m = 0; m < nmma; ++m) {
-                            const uint64_t bd = smem_desc(b_base + m * 2 * TILE_BYTES, TILE_BYTES, 128);
+                const bool partial = wk.head() || wk.tail();
 #pragma unroll
-                            for (int h = 0; h < NH; ++h) {
-                                const uint64_t ad = smem_desc(a_base + (m * NH + h) * A_MMA_BYTES, A_LBO, A_SBO);
-                                umma_f16(tmem_base + buf * C::kAccCols + h * 16, ad, bd, idesc,
-                                         (t0 > wk.seg_s || m > 0) ? 1u : 0u);
+                for (int h = 0; h < NH; ++h) {
+                    const int64_t f = h * SLAB + 32 * q + lane;
+                    if (prm.skip & 4) {
+                    } else if (!partial) {
+                        const int64_t base = (w * TILE_ROWS) * prm.ldc + f;
+#pragma unroll
+                        for (int r = 0; r < 16; ++r) {
+                            const float x = __uint_as_float(v[h][r]);
+                            const int64_t o = base + r * prm.ldc;
+                            if (prm.c_dtype == GRWS_F32) {
+                                asm volatile("st.global.L2::cache_hint.f32 [%0], %1, %2;" ::"l"(static_cast<float *>(prm.C) + o), "f"(x), "l"(pol) : "memory");
+                            } else {
+                                const uint16_t hbits = prm.c_dtype == GRWS_F16 ? __half_as_ushort(__float2half_rn(x))
+                                                                               : __bfloat16_as_ushort(__float2bfloat16_rn(x));
+                                asm volatile("st.global.L2::cache_hint.u16 [%0], %1, %2;" ::"l"(static_cast<uint16_t *>(prm.C) + o), "h"(hbits), "l"(pol) : "memory");
                             }
                         }
-                        umma_commit(smem_u32(&ss->empty_g[gs]));
-                        umma_commit(smem_u32(&ss->empty_m[ms]));
-                        if (t0 + STAGE_TILES >= wk.seg_e) umma_commit(smem_u32(&ss->acc_full[buf]));
                     } else {
-                        raise(prm, ss, ST_TIMEOUT_FULL);
+                        float *slot = prm.partial + (2 * (int64_t)blockIdx.x + (wk.tail() ? 1 : 0)) * (TILE_ROWS * prm.N);
+#pragma unroll
+                        for (int r = 0; r < 16; ++r) slot[(int64_t)r * prm.N + f] = __uint_as_float(v[h][r]);
                     }
                 }
-                ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
             }
+            if (threadIdx.x == EPILOGUE_WARP0 * 32) {       // what the fix-up kernel needs to know
+                int64_t *fx = prm.fix + 4 * (int64_t)blockIdx.x;
+                fx[0] = s; fx[1] = tail_w; fx[2] = tail_b;
+            }
+            if (PROF && prm.dbg && threadIdx.x == EPILOGUE_WARP0 * 32) prm.dbg[blockIdx.x * 16 + 7] = w_af;
         }
-    } else {
-        // ------------------------------------------------------------------ epilogue (warps 4-7)
-        const uint64_t pol = policy_stream();
-        const int q = warp & 3;                        // TMEM lane quarter this warp may read
-        uint32_t ai = 0;
-        bool ok = true;
-        while (ok && wk.next_segment(lane)) {
-            const int64_t w = wk.window();
-            const bool nonempty = wk.seg_e > wk.seg_s;
-            uint32_t v[NH][16];
-            if (nonempty) {
-                const uint32_t buf = ai % NACC, aph = (ai / NACC) & 1u;
-                ++ai;
-                ok = mbar_wait(smem_u32(&ss->acc_full[buf]), aph, abort_flag);
-                ok = __all_sync(0xffffffffu, ok) != 0;
-                if (!ok) { raise(prm, ss, ST_TIMEOUT_ACC); break; }
+    } else if (warp < NUM_PRODUCER_WARPS) {
+        // ------------------------------------------------------------------ gather producers
+        // Two warps per pipeline stage: producer warps 2w and 2w+1 own gather slot w and fill every
+        // kStages-th stage, so the barrier polls and column-id reads of kStages stages overlap.
+        // The rows are fetched by the TMA unit (tile::gather4): a lane issues the copy of four
+        // consecutive slots x 64 features; 16 lanes of each warp cover two of the stage's four
+        // K-steps (TMA instructions of different lanes issue one after the other, so the work of a
+        // stage is split between two warps).  The copies complete on the stage's barrier.
+        static_assert(NUM_PRODUCER_WARPS == 2 * Cfg<NH>::kStages, "two producer warps per gather slot");
+        static_assert(MMAS_PER_STAGE == 4, "lane mapping assumes four K-steps per stage");
+        const uint64_t keep = policy_keep();
+        const int member = warp & 1;
+        const bool issuer = lane < 16;
+        const int m = 2 * member + ((lane >> 3) & 1), grp = (lane >> 1) & 3, half = lane & 1;
+        // slots 4*grp .. 4*grp+3 of K-step m: slot half grp / 2, lines (4*grp) % 8 .. +3 of the atom
+        const uint32_t lane_off = (uint32_t)(m * NH * A_MMA_BYTES + (grp >> 1) * A_SBO + half * A_LBO + ((4 * grp) & 7) * 128);
+        long long w_full_m = 0, w_empty_g = 0;
+        const uint32_t gs = (uint32_t)(warp >> 1);
+        const uint32_t full_bar = smem_u32(&ss->full_g[gs]), empty_bar = smem_u32(&ss->empty_g[gs]);
+        const uint32_t dst = smem_u32(ring_g + (size_t)gs * C::kStageBytes) + lane_off;
+        uint32_t gph = 0;
+        for (uint32_t it = gs;; it += C::kStages, gph ^= 1u) {
+            const uint32_t ms = it % C::kMeta, mph = (it / C::kMeta) & 1u;
+            // column ids and the command have landed
+            bool ok = true;
+            if (lane == 0) ok = mbar_wait_t<PROF>(smem_u32(&ss->full_m[ms]), mph, abort_flag, w_full_m);
+            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+            if (!ok) { if (lane == 0) raise(prm, ss, ST_TIMEOUT_META); break; }
+            if (lane == 0) prof_mark<PROF>(prm.dbg, it, 1);
+            const uint8_t *meta = ring_m + (size_t)ms * META_BYTES;
+            const uint32_t cmd = *reinterpret_cast<const volatile uint32_t *>(meta + META_TILE_BYTES + META_COL_BYTES);
+            const bool end = (cmd & CMD_END) != 0;
+            const int ntiles = end ? 0 : (int)(cmd & 15u);
+            const int nvalid = ntiles * TILE_COLS;               // slots that carry a column id
+            const int nmma = (ntiles + 1) >> 1;
+            // the four column ids of this lane's slots (slots past the last tile read nothing)
+            const int slot0 = 16 * m + 4 * grp;
+            int4 c = *reinterpret_cast<const int4 *>(meta + META_TILE_BYTES + slot0 * 4);
+            if (slot0 >= nvalid) c = make_int4(-1, -1, -1, -1);
+            // the gather slot has been released by the MMA warp (it finished stage it - kStages)
+            if (lane == 0) ok = mbar_wait_t<PROF>(empty_bar, gph ^ 1u, abort_flag, w_empty_g);
+            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+            if (!ok) { if (lane == 0) raise(prm, ss, ST_TIMEOUT_EMPTY); break; }
+            if (lane == 0) prof_mark<PROF>(prm.dbg, it, 2);
+            // ... which also frees the tile / column slot of that older stage for the TMA warp
+            if (lane == 0 && member == 0 && it >= (uint32_t)C::kStages) mbar_arrive(smem_u32(&ss->empty_m[(it - C::kStages) % C::kMeta]));
+            if (end) {                      // pass the end marker on to the MMA warp
+                if (lane == 0 && member == 0) mbar_arrive(full_bar);
+                break;
+            }
+            // bytes the K-steps of this stage bring in: 16 slots x 128 features x NH slabs each
+            if (lane == 0 && member == 0) mbar_expect_tx(full_bar, (uint32_t)(nmma * 16 * SLAB * 2 * NH));
+            if (issuer && m < nmma && !(prm.skip & 2)) {
+#pragma unroll
+                for (int h = 0; h < NH; ++h)
+                    tma_gather4(dst + (uint32_t)(h * A_MMA_BYTES), &b_map, full_bar, h * SLAB + half * 64, c.x, c.y, c.z, c.w, keep);
+            }
+            if (lane == 0) prof_mark<PROF>(prm.dbg, it, 3);
+        }
+        if (PROF && prm.dbg && threadIdx.x == 0) { prm.dbg[blockIdx.x * 16 + 2] = w_full_m; prm.dbg[blockIdx.x * 16 + 3] = w_empty_g; }
+    } else if (warp == MMA_WARP) {
+        // ------------------------------------------------------------------ MMA issuer (one thread)
+        if (lane == 0) {
+            const uint32_t idesc = (1u << 4) | ((uint32_t)prm.is_bf16 << 7) | ((uint32_t)prm.is_bf16 << 10) |
+                                   (1u << 15) | ((16u >> 3) << 17) | ((128u >> 4) << 24);
+            // descriptors of stage 0 / meta slot 0; other stages add their byte offset >> 4 to the low word
+            const uint64_t a_desc0 = smem_desc(smem_u32(ring_g), A_LBO, A_SBO, 2);
+            const uint64_t b_desc0 = smem_desc(smem_u32(ring_m), TILE_BYTES, 128, 0);
+            uint32_t ai = 0, buf = 0;
+            long long w_acc = 0, w_fm = 0, w_fg = 0, t_issue = 0, t_commit = 0;
+            const long long t_mark = prof_clock<PROF>();
+            uint32_t it = 0, gs = 0, gph = 0, ms = 0;
+            for (;; ++it) {
+                // The producers arrive on full_g only after they have seen full_m of the same stage,
+                // so this one wait also covers the tile values and the command word.
+                if (!mbar_wait_t<PROF>(smem_u32(&ss->full_g[gs]), gph, abort_flag, w_fg)) { raise(prm, ss, ST_TIMEOUT_FULL); break; }
+                prof_mark<PROF>(prm.dbg, it, 5);
+                const uint32_t cmd = *reinterpret_cast<const volatile uint32_t *>(ring_m + ms * META_BYTES + META_TILE_BYTES + META_COL_BYTES);
+                if (cmd & CMD_END) break;
+                const int nmma = (int)((cmd & 15u) + 1u) >> 1;
+                if (cmd & CMD_FIRST) {
+                    buf = ai % NACC;
+                    const uint32_t aph = (ai / NACC) & 1u;
+                    ++ai;
+                    if (!mbar_wait_t<PROF>(smem_u32(&ss->acc_empty[buf]), aph ^ 1u, abort_flag, w_acc)) { raise(prm, ss, ST_TIMEOUT_ACC); break; }
+                }
+                // cp.async data is handed over by the mbarrier the producers arrive on after their
+                // copies have landed; no generic->async proxy fence is issued here (it would also
+                // wait for every younger gather in flight)
                 tc_fence_after();
+                const long long ti0 = prof_clock<PROF>();
+                const uint32_t d_tmem = tmem_base + buf * C::kAccCols;
+                const uint64_t ad = a_desc0 + (uint64_t)(gs * (C::kStageBytes >> 4));
+                const uint64_t bd = b_desc0 + (uint64_t)(ms * (META_BYTES >> 4));
+                const uint32_t first = (cmd & CMD_FIRST) ? 0u : 1u;
 #pragma unroll
-                for (int h = 0; h < NH; ++h)
-                    tmem_ld16(tmem_base + ((uint32_t)(32 * q) << 16) + buf * C::kAccCols + h * 16, v[h]);
-                tmem_ld_wait();
-                tc_fence_before();
-                mbar_arrive(smem_u32(&ss->acc_empty[buf]));
-            } else {
+                for (int m = 0; m < MMAS_PER_STAGE; ++m) {
+                    if (m < nmma && !(prm.skip & 1)) {
 #pragma unroll
-                for (int h = 0; h < NH; ++h)
-#pragma unroll
-                    for (int r = 0; r < 16; ++r) v[h][r] = 0u;
-            }
-            const bool partial = wk.head() || wk.tail();
-#pragma unroll
-            for (int h = 0; h < NH; ++h) {
-                const int64_t f = h * SLAB + 32 * q + lane;
-                if (!partial) {
-                    const int64_t base = (w * TILE_ROWS) * prm.ldc + f;
-#pragma unroll
-                    for (int r = 0; r < 16; ++r) {
-                        const float x = __uint_as_float(v[h][r]);
-                        const int64_t o = base + r * prm.ldc;
-                        if (prm.c_dtype == GRWS_F32) {
-                            asm volatile("st.global.L2::cache_hint.f32 [%0], %1, %2;" ::"l"(static_cast<float *>(prm.C) + o), "f"(x), "l"(pol) : "memory");
-                        } else {
-                            const uint16_t hbits = prm.c_dtype == GRWS_F16 ? __half_as_ushort(__float2half_rn(x))
-                                                                           : __bfloat16_as_ushort(__float2bfloat16_rn(x));
-                            asm volatile("st.global.L2::cache_hint.u16 [%0], %1, %2;" ::"l"(static_cast<uint16_t *>(prm.C) + o), "h"(hbits), "l"(pol) : "memory");
-                        }
+                        for (int h = 0; h < NH; ++h)
+                            umma_f16(d_tmem + h * 16, ad + (uint64_t)(((m * NH + h) * A_MMA_BYTES) >> 4),
+                                     bd + (uint64_t)((m * 2 * TILE_BYTES) >> 4), idesc, m > 0 ? 1u : first);
                     }
-                } else {
-                    float *slot = prm.partial + (2 * (int64_t)blockIdx.x + (wk.tail() ? 1 : 0)) * (TILE_ROWS * prm.N);
-#pragma unroll
-                    for (int r = 0; r < 16; ++r) slot[(int64_t)r * prm.N + f] = __uint_as_float(v[h][r]);
                 }
+                const long long ti1 = prof_clock<PROF>();
+                umma_commit(smem_u32(&ss->empty_g[gs]));
+                if (cmd & CMD_LAST) umma_commit(smem_u32(&ss->acc_full[buf]));
+                const long long ti2 = prof_clock<PROF>();
+                t_issue += ti1 - ti0;
+                t_commit += ti2 - ti1;
+                prof_mark<PROF>(prm.dbg, it, 6);
+                if (++gs == (uint32_t)C::kStages) { gs = 0; gph ^= 1u; }
+                if (++ms == (uint32_t)C::kMeta) ms = 0;
+            }
+            if (PROF && prm.dbg) {
+                long long *d = prm.dbg + blockIdx.x * 16;
+                d[4] = w_acc; d[5] = w_fm; d[6] = w_fg; d[8] = t_issue; d[9] = t_commit; d[10] = prof_clock<PROF>() - t_mark; d[11] = it;
             }
         }
+        __syncwarp();
     }
 
     // teardown: everybody meets, then the allocating warp frees tensor memory
     tc_fence_before();
     __syncthreads();
-    if (warp == 8) {
+    if (warp == MMA_WARP) {
         tc_fence_after();
         tmem_dealloc(tmem_base, C::kTmemCols);
     }
 }
 
-// Sums the partial tiles of windows cut by a CTA boundary (same rule as the warp path's fix-up,
-// with the chunk derived from the live tile count and the grid size).
+// Sums the partial tiles of the windows that were split between CTAs, in CTA order.  CTA k of the
+// main kernel recorded whether it holds the first piece of a split window (and where that window
+// ends) and every CTA recorded where its tile range starts; the following CTAs whose range starts
+// inside the window hold its other pieces.
 __global__ void __launch_bounds__(128)
 spmm_tc5_fixup_kernel(const Params prm, int64_t G) {
-    __shared__ int64_t sh[3];
-    const int64_t k = (int64_t)blockIdx.x + 1;
-    const int64_t W = prm.W, N = prm.N;
-    const int64_t T = __ldg(prm.window_offset + W);
-    int64_t chunk = (T + G - 1) / G;
-    chunk = (chunk + 1) & ~int64_t(1);
-    if (chunk < 2) chunk = 2;
-    const int64_t x = k * chunk;
-    if (x >= T) return;
-    if (threadIdx.x < 32) {
-        int64_t w = warp_count_ends_le(prm.window_offset, W, x, threadIdx.x);
-        if (threadIdx.x == 0) {
-            sh[0] = w;
-            sh[1] = __ldg(prm.window_offset + w);
-            sh[2] = __ldg(prm.window_offset + w + 1);
-        }
-    }
-    __syncthreads();
-    const int64_t w = sh[0], a = sh[1], b = sh[2];
-    if (x <= a) return;                       // the cut coincides with the window start
-    if (a / chunk + 1 != k) return;           // an earlier cut inside this window sums it
-    const int64_t k_last = (b - 1) / chunk;
-    const int64_t elems = TILE_ROWS * N;
+    const int64_t k = blockIdx.x;
+    const int64_t *fx = prm.fix + 4 * k;
+    const int64_t w = fx[1];
+    if (w < 0) return;
+    const int64_t b = fx[2];
+    int64_t k_last = k;
+    while (k_last + 1 < G && prm.fix[4 * (k_last + 1)] < b) ++k_last;
+    const int64_t N = prm.N, elems = TILE_ROWS * N;
     for (int64_t i = threadIdx.x; i < elems; i += blockDim.x) {
-        float v = prm.partial[(2 * (k - 1) + 1) * elems + i];
-        for (int64_t q = k; q <= k_last; ++q) v += prm.partial[(2 * q) * elems + i];
+        float v = prm.partial[(2 * k + 1) * elems + i];                                   // first piece
+        for (int64_t q = k + 1; q <= k_last; ++q) v += prm.partial[(2 * q) * elems + i];   // later pieces
         const int64_t r = i / N, f = i % N;
         const int64_t o = (w * TILE_ROWS + r) * prm.ldc + f;
         if (prm.c_dtype == GRWS_F32) static_cast<float *>(prm.C)[o] = v;
@@ -503,7 +610,56 @@ static int grid_size() {
 }
 
 constexpr size_t STATUS_BYTES = 256;
+constexpr size_t DEBUG_BYTES = 512 * 16 * sizeof(long long);
+constexpr size_t FIX_BYTES = 512 * 4 * sizeof(int64_t);      // per-CTA fix-up records   // per-CTA wait counters (GRWS_TC5_PROFILE=1)
 
+static bool profile_waits() {
+    static const int v = [] { const char *e = getenv("GRWS_TC5_PROFILE"); return e ? atoi(e) : 0; }();
+    return v != 0;
+}
+
+}  // namespace tc5
+
+namespace tc5 {
+template <int NH>
+static cudaError_t launch_kernel(const Params &prm, const CUtensorMap &b_map, int G, cudaStream_t stream) {
+    static const cudaError_t attr = [] {
+        cudaError_t e = cudaFuncSetAttribute(spmm_tc5_kernel<NH, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<NH>::kSmem);
+        if (e != cudaSuccess) return e;
+        return cudaFuncSetAttribute(spmm_tc5_kernel<NH, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<NH>::kSmem);
+    }();
+    if (attr != cudaSuccess) return attr;
+    if (prm.dbg) spmm_tc5_kernel<NH, true><<<G, NUM_THREADS, Cfg<NH>::kSmem, stream>>>(prm, b_map);
+    else spmm_tc5_kernel<NH, false><<<G, NUM_THREADS, Cfg<NH>::kSmem, stream>>>(prm, b_map);
+    return cudaSuccess;
+}
+
+// Tensor map of the dense operand for the row gathers: 2-D [K rows][N features], box of one row
+// by 64 features (128 bytes), 128-byte swizzle, zero fill outside the tensor.
+static int encode_b_map(CUtensorMap *map, const void *B, int is_bf16, int64_t K, int64_t N, int64_t ldb) {
+    typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                 const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                 CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static EncodeFn encode = [] {
+        void *fn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            fn = nullptr;
+        return reinterpret_cast<EncodeFn>(fn);
+    }();
+    if (!encode) return fail(GRWS_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    const cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)(K > 0 ? K : 1)};
+    const cuuint64_t strides[1] = {(cuuint64_t)ldb * 2};
+    const cuuint32_t box[2] = {64, 1};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = encode(map, is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+                              const_cast<void *>(B), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(GRWS_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    return GRWS_OK;
+}
 }  // namespace tc5
 
 bool spmm_tc5_supported(int dtype, int64_t N) {
@@ -513,7 +669,7 @@ bool spmm_tc5_supported(int dtype, int64_t N) {
 
 size_t spmm_tc5_scratch_bytes(int64_t num_tiles_bound, int64_t N) {
     (void)num_tiles_bound;
-    return tc5::STATUS_BYTES + (size_t)tc5::grid_size() * 2 * TILE_ROWS * (size_t)N * sizeof(float);
+    return tc5::STATUS_BYTES + tc5::DEBUG_BYTES + tc5::FIX_BYTES + (size_t)tc5::grid_size() * 2 /* CTAs per SM */ * 2 * TILE_ROWS * (size_t)N * sizeof(float);
 }
 
 int spmm_tc5_launch(const int64_t *window_offset, const int32_t *cols, const void *vals, int dtype,
@@ -521,30 +677,26 @@ int spmm_tc5_launch(const int64_t *window_offset, const int32_t *cols, const voi
                     int64_t num_tiles_bound, int64_t K, int64_t N, void *scratch, size_t scratch_bytes,
                     cudaStream_t stream) {
     using namespace tc5;
-    (void)K;
     const size_t need = spmm_tc5_scratch_bytes(num_tiles_bound, N);
     if (scratch_bytes < need || scratch == nullptr)
         return fail(GRWS_ERR_SCRATCH, "spmm scratch too small: %zu < %zu bytes", scratch_bytes, need);
     Params prm;
     prm.window_offset = window_offset; prm.cols = cols; prm.vals = vals; prm.B = B; prm.C = C;
     prm.status = static_cast<int *>(scratch);
-    prm.partial = reinterpret_cast<float *>(static_cast<char *>(scratch) + STATUS_BYTES);
+    { static const int sk = [] { const char *e = getenv("GRWS_TC5_SKIP"); return e ? atoi(e) : 0; }(); prm.skip = sk; }
+    prm.dbg = profile_waits() ? reinterpret_cast<long long *>(static_cast<char *>(scratch) + STATUS_BYTES) : nullptr;
+    prm.fix = reinterpret_cast<int64_t *>(static_cast<char *>(scratch) + STATUS_BYTES + DEBUG_BYTES);
+    prm.partial = reinterpret_cast<float *>(static_cast<char *>(scratch) + STATUS_BYTES + DEBUG_BYTES + FIX_BYTES);
     prm.W = W; prm.N = N; prm.ldb = ldb; prm.ldc = ldc; prm.c_dtype = c_dtype;
     prm.is_bf16 = dtype == GRWS_BF16 ? 1 : 0;
-    const int G = grid_size();
+    const int G = grid_size() * (N == 128 ? Cfg<1>::kCtasPerSm : Cfg<2>::kCtasPerSm);
     GRWS_CUDA_TRY(cudaMemsetAsync(scratch, 0, STATUS_BYTES, stream));
-    if (N == 128) {
-        static const cudaError_t attr = cudaFuncSetAttribute(spmm_tc5_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<1>::kSmem);
-        GRWS_CUDA_TRY(attr);
-        spmm_tc5_kernel<1><<<G, NUM_THREADS, Cfg<1>::kSmem, stream>>>(prm);
-    } else {
-        static const cudaError_t attr = cudaFuncSetAttribute(spmm_tc5_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<2>::kSmem);
-        GRWS_CUDA_TRY(attr);
-        spmm_tc5_kernel<2><<<G, NUM_THREADS, Cfg<2>::kSmem, stream>>>(prm);
-    }
+    alignas(64) CUtensorMap b_map;
+    if (int st = encode_b_map(&b_map, B, prm.is_bf16, K, N, ldb)) return st;
+    GRWS_CUDA_TRY((N == 128 ? launch_kernel<1>(prm, b_map, G, stream) : launch_kernel<2>(prm, b_map, G, stream)));
     GRWS_CUDA_TRY(cudaGetLastError());
     if (G > 1) {
-        spmm_tc5_fixup_kernel<<<G - 1, 128, 0, stream>>>(prm, (int64_t)G);
+        spmm_tc5_fixup_kernel<<<G, 128, 0, stream>>>(prm, (int64_t)G);
         GRWS_CUDA_TRY(cudaGetLastError());
     }
     return GRWS_OK;

@@ -122,6 +122,73 @@ int grws_bcsr_transpose_fill(const int64_t *window_offset, const int32_t *cols, 
                              const int64_t *row_ptr_t, int32_t *out_col, float *out_val,
                              void *scratch, size_t scratch_bytes, void *stream);
 
+/* ------------------------------------------------------------------------------------------
+ * BCSR -> CSR of the same matrix (rows ascending in column id): the sampler walks CSR rows.
+ * No counterpart in the reference, whose sampler reads the BCSR tiles directly
+ * (core/include/sampling.cuh:188-394).  count writes row_ptr int64 [num_rows+1]; the caller
+ * reads its last entry (nnz) and allocates out_col int32 [nnz], out_val fp32 [nnz] for fill.
+ * ------------------------------------------------------------------------------------------ */
+size_t grws_bcsr_to_csr_scratch_bytes(int64_t num_rows);
+
+int grws_bcsr_to_csr_count(const int64_t *window_offset, const int32_t *cols, const void *vals,
+                           int val_dtype, int64_t num_windows, int64_t num_rows, int64_t *row_ptr,
+                           void *scratch, size_t scratch_bytes, void *stream);
+
+int grws_bcsr_to_csr_fill(const int64_t *window_offset, const int32_t *cols, const void *vals,
+                          int val_dtype, int64_t num_windows, int64_t num_rows,
+                          const int64_t *row_ptr, int32_t *out_col, float *out_val, void *stream);
+
+/* ------------------------------------------------------------------------------------------
+ * One hop of neighbour sampling.  Replaces Phase 1 of sample_one_layer_internal
+ * (core/wrapper/sampling_wrapper.cu:101-157, warp_centric_find_top_k_kernel,
+ * core/include/sampling.cuh:65-448) with different semantics: the reference keeps, per 16-row
+ * window, the top-K columns by edge weight; this samples, per frontier node, `fanout`
+ * neighbours uniformly without replacement from a Philox4x32-10 stream keyed by
+ * (seed, node, hop) -- counter {node, hop, j/2, 0}, key = seed, draw j = words (2(j&1)+1 :
+ * 2(j&1)).  Degree <= fanout takes all neighbours in CSR order; otherwise Floyd's subset
+ * algorithm with pick_j = floor(draw_j * (deg - fanout + j + 1) / 2^64).  One warp per node.
+ *   nodes int32 [num_nodes] (-1 entries give an empty list); 1 <= fanout <= 256;
+ *   out_nbr int32 [num_nodes*fanout] (-1 padding), out_w fp32 [num_nodes*fanout] (CSR values
+ *   of the picked edges, 1.0 when values is NULL), out_cnt int32 [num_nodes] or NULL.
+ * ------------------------------------------------------------------------------------------ */
+int grws_sample_hop(const int64_t *row_ptr, const int32_t *col_idx, const float *values,
+                    const int32_t *nodes, int64_t num_nodes, int fanout, uint64_t seed, uint32_t hop,
+                    int32_t *out_nbr, float *out_w, int32_t *out_cnt, void *stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Dedup + reindex of a hop.  Replaces prepare_windows_and_masks + the per-layer
+ * reindex_bcsr call (core/wrapper/sampling_wrapper.cu:283-347, models/model.py:127-143) for
+ * per-node sampling: the hop's source list is the destination nodes, in the given order,
+ * followed by the sampled neighbours that are not destination nodes in ascending id order; the
+ * local id of a node is its position in that list.
+ *   out_src     int32 [n_dst + n_dst*fanout]  source list (the first out_counts[0] entries)
+ *   out_local   int32 [n_dst*fanout]          local id of every sampled neighbour, -1 for empty
+ *   out_row_ptr int64 [n_dst+1]               prefix sum of the valid entries per destination
+ *   out_counts  int64 [2]                     {number of source nodes, number of sampled edges}
+ * ------------------------------------------------------------------------------------------ */
+size_t grws_dedup_scratch_bytes(int64_t n_dst, int fanout);
+
+int grws_dedup_reindex(const int32_t *dst, int64_t n_dst, const int32_t *nbr, int fanout,
+                       int32_t *out_src, int32_t *out_local, int64_t *out_row_ptr,
+                       int64_t *out_counts, void *scratch, size_t scratch_bytes, void *stream);
+
+/* Fixed-stride (local id, weight) lists -> compact CSR arrays of the hop's block, which
+ * grws_csr_to_bcsr_* turns into the BCSR block (this replaces build_col_to_val_map_kernel +
+ * recompress_sampled_bcsr_kernel, core/include/sampling.cuh:471-579,707-773). */
+int grws_block_compact(const int32_t *local, const float *w, int64_t n_dst, int fanout,
+                       const int64_t *row_ptr, int32_t *out_col, float *out_val, void *stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Global -> local column ids by window lookup, pruning misses.  Replaces reindex_bcsr_cuda +
+ * reindex_and_prune_kernel (core/wrapper/reindex_wrapper.cu:27-68, core/include/reindex.cuh:
+ * 33-102) with identical integer arithmetic: window = col / tile_rows (C division, so -1 maps
+ * to window 0); hit -> rank * tile_rows + col % tile_rows; miss -> 0 and that column of the
+ * tile's values zeroed in place.
+ * ------------------------------------------------------------------------------------------ */
+int grws_reindex_bcsr(const int32_t *in_cols, void *values, int val_dtype,
+                      const int32_t *active_windows, int64_t num_indices, int64_t num_active,
+                      int tile_rows, int tile_cols, int32_t *out_cols, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

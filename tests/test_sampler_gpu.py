@@ -1,0 +1,122 @@
+"""GPU sampler against the host Philox replay: neighbour lists, dedup / reindex and the per-hop
+BCSR blocks are all bit-exact; the selection is uniform (chi-square)."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def graph():
+    from graph_rws_b200.data import synthetic
+    return synthetic.sym_normalized_csr(5000, *synthetic.chung_lu_edges(5000, 60000, 2.3, 31))
+
+
+def _dev_csr(g):
+    dev = torch.device("cuda")
+    return (torch.from_numpy(g.row_ptr).to(dev), torch.from_numpy(g.col_idx).to(dev), torch.from_numpy(g.values).to(dev))
+
+
+@pytest.mark.parametrize("fanout", [1, 5, 15, 32, 40, 200])
+def test_sample_hop_is_bit_exact(oracle, graph, fanout):
+    from graph_rws_b200 import core
+    rp, ci, vv = _dev_csr(graph)
+    rng = np.random.default_rng(fanout)
+    nodes = rng.permutation(graph.num_nodes)[:700].astype(np.int32)
+    nodes[5] = -1                                     # an empty entry
+    nbr, w, cnt = core.sample_hop(rp, ci, vv, torch.from_numpy(nodes).cuda(), fanout, seed=0x5EED, hop=2)
+    nbr_r, w_r, cnt_r = oracle.sample_hop(graph.row_ptr, graph.col_idx, graph.values, nodes, fanout, 0x5EED, 2)
+    assert np.array_equal(nbr.cpu().numpy(), nbr_r)
+    assert np.array_equal(w.cpu().numpy(), w_r)
+    assert np.array_equal(cnt.cpu().numpy(), cnt_r)
+
+
+def test_sample_hop_does_not_depend_on_batch(graph):
+    from graph_rws_b200 import core
+    rp, ci, vv = _dev_csr(graph)
+    a = torch.arange(0, 3000, 3, dtype=torch.int32, device="cuda")
+    n1, _, _ = core.sample_hop(rp, ci, vv, a, 10, seed=7, hop=1)
+    n2, _, _ = core.sample_hop(rp, ci, vv, a.flip(0).contiguous(), 10, seed=7, hop=1)
+    assert torch.equal(n1, n2.flip(0))
+    n3, _, _ = core.sample_hop(rp, ci, vv, a, 10, seed=8, hop=1)
+    assert not torch.equal(n1, n3)
+
+
+def test_uniformity_chi_square():
+    from graph_rws_b200 import core
+    deg, fanout, trials = 40, 5, 4000
+    rp = torch.tensor([0, deg], dtype=torch.int64, device="cuda")
+    ci = torch.arange(deg, dtype=torch.int32, device="cuda")
+    node = torch.zeros(1, dtype=torch.int32, device="cuda")
+    counts = np.zeros(deg)
+    for s in range(trials):
+        nbr, _, _ = core.sample_hop(rp, ci, None, node, fanout, seed=1000 + s, hop=0)
+        counts[nbr[0].cpu().numpy()] += 1
+    expect = trials * fanout / deg
+    assert ((counts - expect) ** 2 / expect).sum() < 72.1          # chi-square, 39 dof, p = 0.001
+
+
+def test_block_build_is_bit_exact(oracle, graph):
+    from graph_rws_b200 import core
+    rp, ci, vv = _dev_csr(graph)
+    rng = np.random.default_rng(3)
+    dst = rng.permutation(graph.num_nodes)[:333].astype(np.int32)
+    nbr_r, w_r, _ = oracle.sample_hop(graph.row_ptr, graph.col_idx, graph.values, dst, 7, 99, 0)
+    src_r, wo_r, cols_r, vals_r = oracle.build_block(dst, nbr_r, w_r)
+    src, wo, cols, vals = core.build_block(torch.from_numpy(dst).cuda(), torch.from_numpy(nbr_r).cuda(),
+                                           torch.from_numpy(w_r).cuda())
+    assert np.array_equal(src.cpu().numpy(), src_r)
+    assert np.array_equal(wo.cpu().numpy(), wo_r)
+    assert np.array_equal(cols.cpu().numpy(), cols_r)
+    assert np.array_equal(vals.cpu().numpy().view(np.uint32), vals_r.view(np.uint32))
+
+
+def test_multi_hop_sampler_matches_replay(oracle, graph):
+    """BCSRSampler.sample_layers over a BCSRGraph: CSR extraction + 3 hops + blocks, all bit-exact."""
+    from graph_rws_b200 import BCSRGraph
+    from graph_rws_b200.sampler import BCSRSampler
+    g = BCSRGraph.from_csr(graph.num_nodes, graph.row_ptr, graph.col_idx, graph.values, device=torch.device("cuda"))
+    rp, ci, vv = BCSRSampler.graph_csr(g)
+    assert np.array_equal(rp.cpu().numpy(), graph.row_ptr)
+    assert np.array_equal(ci.cpu().numpy(), graph.col_idx)
+    assert np.array_equal(vv.cpu().numpy(), graph.values)
+    seeds = np.random.default_rng(1).permutation(graph.num_nodes)[:256].astype(np.int32)
+    sampler = BCSRSampler(fanouts=[15, 10, 5], verbose=False, seed=0x5EED)
+    layers = sampler.sample_layers(g, torch.from_numpy(seeds))
+    blocks = oracle.sample_layers(graph.row_ptr, graph.col_idx, graph.values, seeds, [15, 10, 5], 0x5EED)
+    assert len(layers) == 3
+    for sub, ref in zip(layers, blocks):
+        assert np.array_equal(sub.output_nodes.cpu().numpy(), ref["dst"])
+        assert np.array_equal(sub.input_nodes.cpu().numpy(), ref["src"])
+        assert sub.num_rows == ref["dst"].size and sub.num_cols == ref["src"].size
+        assert np.array_equal(sub.window_offset.cpu().numpy(), ref["window_offset"])
+        assert np.array_equal(sub.original_col_indices.cpu().numpy(), ref["cols"])
+        assert np.array_equal(sub.values_condensed.cpu().numpy(), ref["vals"])
+    assert np.array_equal(layers[-1].output_nodes.cpu().numpy(), seeds)
+    # target-first layout: a block's rows are the first entries of its columns
+    for sub in layers:
+        assert torch.equal(sub.input_nodes[:sub.num_rows], sub.output_nodes)
+
+
+def test_reference_named_sampling_entry_points(oracle, graph):
+    from graph_rws_b200 import BCSRGraph, core
+    g = BCSRGraph.from_csr(graph.num_nodes, graph.row_ptr, graph.col_idx, graph.values, device=torch.device("cuda"))
+    seeds = torch.arange(100, 164, dtype=torch.int32, device="cuda")
+    dummy = torch.ones(1, device="cuda")
+    layers, timings = core.sample_all_layers(g.window_offset, g.original_col_indices, g.values_condensed, seeds,
+                                             [5, 10], g.num_nodes, dummy, dummy.int(), dummy.int(), dummy.int())
+    assert len(layers) == 2 and len(layers[0]) == 5 and len(timings) == 2
+    assert timings[0].total_time >= 0 and "total_time" in timings[0].to_dict()
+    blocks = oracle.sample_layers(graph.row_ptr, graph.col_idx, graph.values, seeds.cpu().numpy(), [10, 5], 0x5EED)
+    assert np.array_equal(layers[0][4].cpu().numpy(), blocks[1]["src"])       # hop 0 = the seeds' hop
+    assert np.array_equal(layers[1][1].cpu().numpy(), blocks[0]["cols"])
+    # reindex_bcsr: reference semantics including pruning and the -1 quirk
+    cols = torch.tensor([37, 83, 100, -1, 80, 95, 32, 47], dtype=torch.int32, device="cuda")
+    vals = (torch.arange(128, dtype=torch.float32, device="cuda") + 1)
+    new = core.reindex_bcsr(cols, vals, torch.tensor([2, 5], dtype=torch.int32, device="cuda"))
+    new_r, vals_r = oracle.reindex(cols.cpu().numpy(), (np.arange(128) + 1).astype(np.float32), np.array([2, 5], np.int32))
+    assert np.array_equal(new.cpu().numpy(), new_r) and np.array_equal(vals.cpu().numpy(), vals_r)
+    new2 = core.reindex_bcsr(torch.tensor([-1, 3] * 4, dtype=torch.int32, device="cuda"), torch.ones(128, device="cuda"),
+                             torch.tensor([0], dtype=torch.int32, device="cuda"))
+    assert new2.cpu().tolist() == [-1, 3] * 4
