@@ -77,6 +77,7 @@ struct Params {
     int64_t W, N, ldb, ldc;
     int c_dtype;
     int is_bf16;
+    int lw_shift;     // a cut inside a window of at most chunk >> lw_shift tiles moves to the window start
     int skip;         // experiment knob (GRWS_TC5_SKIP): 1 = issue no MMAs, 2 = gather nothing, 4 = no output stores
     long long *dbg;   // optional [grid][16] cycle counters (wait time per role), null when not profiling
 };
@@ -312,8 +313,8 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
         chunk = (chunk + 1) & ~int64_t(1);
         if (chunk < 2) chunk = 2;
         // a cut inside a window of at most chunk/16 tiles moves back to that window's start, so
-        // only long windows are ever split between CTAs (tile counts stay balanced within 1/16)
-        const int64_t long_window = chunk >> 4;
+        // only long windows are ever split between CTAs (tile counts stay balanced within chunk >> lw_shift)
+        const int64_t long_window = chunk >> prm.lw_shift;
         int64_t w_first, w_unused;
         const int64_t s = warp_cut(prm.window_offset, W, T, blockIdx.x, G, chunk, long_window, lane, &w_first);
         const int64_t e = warp_cut(prm.window_offset, W, T, (int64_t)blockIdx.x + 1, G, chunk, long_window, lane, &w_unused);
@@ -684,6 +685,7 @@ int spmm_tc5_launch(const int64_t *window_offset, const int32_t *cols, const voi
     prm.window_offset = window_offset; prm.cols = cols; prm.vals = vals; prm.B = B; prm.C = C;
     prm.status = static_cast<int *>(scratch);
     { static const int sk = [] { const char *e = getenv("GRWS_TC5_SKIP"); return e ? atoi(e) : 0; }(); prm.skip = sk; }
+    { static const int lw = [] { const char *e = getenv("GRWS_TC5_LW_SHIFT"); return e ? atoi(e) : 4; }(); prm.lw_shift = lw; }
     prm.dbg = profile_waits() ? reinterpret_cast<long long *>(static_cast<char *>(scratch) + STATUS_BYTES) : nullptr;
     prm.fix = reinterpret_cast<int64_t *>(static_cast<char *>(scratch) + STATUS_BYTES + DEBUG_BYTES);
     prm.partial = reinterpret_cast<float *>(static_cast<char *>(scratch) + STATUS_BYTES + DEBUG_BYTES + FIX_BYTES);

@@ -1,0 +1,18 @@
+"""One process per GPU over torch.distributed (NCCL on NVLink / NVSwitch; gloo in the CPU tests).
+
+The reference is single-GPU (helper/utils.py:19-24); this module covers the two places where its
+hot path shards naturally:
+
+* full-graph SpMM: contiguous window ranges per rank, balanced by tile count; every rank owns
+  the matching rows of the dense operands; one all-gather of H before the local product (and one
+  of G before the local rows of the transposed product);
+* sampled training: seeds are sharded per rank, sampling is keyed by (seed, node, hop) so the
+  result does not depend on the number of ranks; feature rows of a hop's input nodes are
+  fetched from the ranks that own them.
+
+Nothing here issues a TMA multicast load, and no kernel is handed a peer GPU's memory: remote
+rows land in local HBM through the collective first.
+"""
+from .row_partition import (RowPartition, all_gather_rows, partition_windows_by_tiles,  # noqa: F401
+                            shard_bcsr, DistributedSpMM)
+from .seed_shard import exchange_rows, owner_of, shard_seeds  # noqa: F401

@@ -1,0 +1,98 @@
+"""Row-partitioned full-graph SpMM: window ranges per rank, all-gather of the dense operand."""
+from dataclasses import dataclass
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+
+
+@dataclass
+class RowPartition:
+    """Contiguous window range [w_begin, w_end) of every rank and the matching row ranges."""
+    window_bounds: List[int]       # world + 1 entries
+    num_rows: int
+
+    @property
+    def world(self) -> int:
+        return len(self.window_bounds) - 1
+
+    def windows(self, rank: int):
+        return self.window_bounds[rank], self.window_bounds[rank + 1]
+
+    def rows(self, rank: int):
+        lo, hi = self.windows(rank)
+        return min(lo * 16, self.num_rows), min(hi * 16, self.num_rows)
+
+    def max_rows(self) -> int:
+        return max(self.rows(r)[1] - self.rows(r)[0] for r in range(self.world))
+
+
+def partition_windows_by_tiles(window_offset: torch.Tensor, world: int, num_rows: Optional[int] = None) -> RowPartition:
+    """Cut the windows into ``world`` contiguous ranges of (nearly) equal TILE count: the SpMM cost
+    of a window is its tile count, and power-law graphs make window counts a poor proxy."""
+    wo = window_offset.detach().cpu().to(torch.int64)
+    W = wo.numel() - 1
+    T = int(wo[-1])
+    bounds = [0]
+    for r in range(1, world):
+        target = (T * r) // world
+        # first window whose start is >= target, never behind the previous cut
+        w = int(torch.searchsorted(wo[:-1].contiguous(), torch.tensor(target), right=False))
+        bounds.append(min(max(w, bounds[-1]), W))
+    bounds.append(W)
+    return RowPartition(bounds, W * 16 if num_rows is None else int(num_rows))
+
+
+def shard_bcsr(window_offset, cols, vals, part: RowPartition, rank: int):
+    """The rank's slice of a BCSR graph: same column ids (global), local windows."""
+    lo, hi = part.windows(rank)
+    t0, t1 = int(window_offset[lo]), int(window_offset[hi])
+    wo = (window_offset[lo:hi + 1] - t0).contiguous()
+    return wo, cols[t0 * 8:t1 * 8].contiguous(), vals[t0 * 128:t1 * 128].contiguous()
+
+
+def all_gather_rows(local: torch.Tensor, part: RowPartition, group=None) -> torch.Tensor:
+    """All-gather the row shards of a dense matrix into the full [num_rows, N] matrix.
+
+    Shards may differ in size, so each rank contributes ``max_rows`` rows (zero padded) to one
+    ``all_gather_into_tensor`` and the valid parts are copied out."""
+    world = part.world
+    if world == 1:
+        return local
+    pad_rows = part.max_rows()
+    n = local.shape[1]
+    send = local
+    if local.shape[0] != pad_rows:
+        send = torch.zeros((pad_rows, n), dtype=local.dtype, device=local.device)
+        send[:local.shape[0]] = local
+    recv = torch.empty((world * pad_rows, n), dtype=local.dtype, device=local.device)
+    dist.all_gather_into_tensor(recv, send.contiguous(), group=group)
+    if all(part.rows(r)[1] - part.rows(r)[0] == pad_rows for r in range(world)):
+        return recv[:part.num_rows]
+    full = torch.empty((part.num_rows, n), dtype=local.dtype, device=local.device)
+    for r in range(world):
+        lo, hi = part.rows(r)
+        full[lo:hi] = recv[r * pad_rows:r * pad_rows + (hi - lo)]
+    return full
+
+
+class DistributedSpMM:
+    """C_local = A[rows of this rank, :] @ H for H sharded by the same row partition
+    (a square, symmetric-pattern adjacency: rows and columns share one node numbering)."""
+
+    def __init__(self, graph, part: RowPartition, rank: int, group=None):
+        from ..data import BCSRGraph
+        self.part, self.rank, self.group = part, rank, group
+        wo, cols, vals = shard_bcsr(graph.window_offset, graph.original_col_indices, graph.values_condensed, part, rank)
+        lo, hi = part.rows(rank)
+        self.local = BCSRGraph(num_nodes=hi - lo, num_edges=None, tile_rows=16, tile_cols=8, window_offset=wo,
+                               original_col_indices=cols, values_condensed=vals, device=vals.device,
+                               num_rows=hi - lo, num_cols=part.num_rows, values_dtype=vals.dtype)
+
+    def __call__(self, h_local: torch.Tensor) -> torch.Tensor:
+        from .. import core
+        h_full = all_gather_rows(h_local, self.part, self.group)
+        g = self.local
+        out = core.spmm_raw(g.window_offset, g.original_col_indices, g.values_as(h_full.dtype), h_full.contiguous())
+        lo, hi = self.part.rows(self.rank)
+        return out[:hi - lo]
