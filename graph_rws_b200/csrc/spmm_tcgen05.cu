@@ -579,7 +579,7 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
 // main kernel recorded whether it holds the first piece of a split window (and where that window
 // ends) and every CTA recorded where its tile range starts; the following CTAs whose range starts
 // inside the window hold its other pieces.
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(1024)
 spmm_tc5_fixup_kernel(const Params prm, int64_t G) {
     const int64_t k = blockIdx.x;
     const int64_t *fx = prm.fix + 4 * k;
@@ -589,6 +589,8 @@ spmm_tc5_fixup_kernel(const Params prm, int64_t G) {
     int64_t k_last = k;
     while (k_last + 1 < G && prm.fix[4 * (k_last + 1)] < b) ++k_last;
     const int64_t N = prm.N, elems = TILE_ROWS * N;
+    // one or two elements per thread: the loads of a thread are a dependent chain, so the kernel's
+    // duration is that chain's length, not the (tiny) amount of data
     for (int64_t i = threadIdx.x; i < elems; i += blockDim.x) {
         float v = prm.partial[(2 * k + 1) * elems + i];                                   // first piece
         for (int64_t q = k + 1; q <= k_last; ++q) v += prm.partial[(2 * q) * elems + i];   // later pieces
@@ -698,7 +700,7 @@ int spmm_tc5_launch(const int64_t *window_offset, const int32_t *cols, const voi
     GRWS_CUDA_TRY((N == 128 ? launch_kernel<1>(prm, b_map, G, stream) : launch_kernel<2>(prm, b_map, G, stream)));
     GRWS_CUDA_TRY(cudaGetLastError());
     if (G > 1) {
-        spmm_tc5_fixup_kernel<<<G, 128, 0, stream>>>(prm, (int64_t)G);
+        spmm_tc5_fixup_kernel<<<G, 1024, 0, stream>>>(prm, (int64_t)G);
         GRWS_CUDA_TRY(cudaGetLastError());
     }
     return GRWS_OK;
