@@ -23,6 +23,8 @@ SIGNATURES = {
     "grws_spmm_resolve_algo": (c_i32, [c_i32, c_i64, c_i32]),
     "grws_spmm_fwd": (c_i32, [c_vp, c_vp, c_vp, c_i32, c_vp, c_i32, c_i64, c_vp, c_i32, c_i64,
                               c_i64, c_i64, c_i64, c_i64, c_vp, c_sz, c_i32, c_vp]),
+    "grws_spmm_fwd_static": (c_i32, [c_vp, c_vp, c_vp, c_i32, c_vp, c_i32, c_i64, c_vp, c_i32, c_i64,
+                                     c_i64, c_i64, c_i64, c_i64, c_vp]),
     "grws_csr_to_bcsr_scratch_bytes": (c_sz, [c_i64, c_i64]),
     "grws_csr_to_bcsr_count": (c_i32, [c_i64, c_vp, c_vp, c_vp, c_i64, c_vp, c_vp, c_sz, c_vp]),
     "grws_csr_to_bcsr_fill": (c_i32, [c_i64, c_i64, c_vp, c_i64, c_vp, c_vp, c_i32, c_vp, c_sz, c_vp]),

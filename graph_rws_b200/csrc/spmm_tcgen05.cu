@@ -707,3 +707,82 @@ int spmm_tc5_launch(const int64_t *window_offset, const int32_t *cols, const voi
 }
 
 }  // namespace grws
+
+// ---------------------------------------------------------------------------------------------
+// Forward SpMM for callers that must not allocate device memory.
+//
+// Some hosts of this library cannot call cudaMalloc around an SpMM: a plugin that runs inside
+// another framework's stream-ordered or pooled allocator and is handed only its input and output
+// buffers, a real-time inference loop whose memory was frozen at start-up, a caller that is in
+// the middle of capturing work it does not own.  For them the scratch of the tcgen05 kernel (its
+// status word, the per-CTA fix-up records and the fp32 partial tiles of windows that were split
+// between CTAs) lives in the fixed array below instead of a caller-provided buffer.
+//
+//   * The array is STATIC_SCRATCH_BYTES (about 11 MB) and every GPU that loads the library keeps
+//     it until the process exits.  It is sized for dense widths up to 256 on a device with up to
+//     160 SMs; anything that would need more is rejected with GRWS_ERR_SCRATCH.
+//   * In host code the array's name is only a host-side handle, not a device address.  The device
+//     address is looked up with cudaGetSymbolAddress, once per device, with that device current,
+//     on the first call made on that device -- so make that first call before any stream capture.
+//   * All calls share the array and it keeps the last call's contents: the status word is cleared
+//     on the stream before each launch, everything else is written before it is read within a
+//     call.  Two calls that overlap on the GPU (different streams, or one device used from two
+//     threads) race on it; serialise them or use grws_spmm_fwd with separate scratch buffers.
+//   * No cudaMalloc, cudaFree or allocating library routine is called.
+// ---------------------------------------------------------------------------------------------
+namespace grws {
+namespace tc5 {
+
+constexpr int STATIC_MAX_SMS = 160;
+constexpr int STATIC_MAX_N = 256;
+constexpr size_t STATIC_SCRATCH_BYTES =
+    STATUS_BYTES + DEBUG_BYTES + FIX_BYTES + (size_t)STATIC_MAX_SMS * 2 * 2 * TILE_ROWS * STATIC_MAX_N * sizeof(float);
+static_assert(STATIC_SCRATCH_BYTES == GRWS_SPMM_STATIC_SCRATCH_BYTES, "the header states the size of the built-in scratch");
+
+static __device__ __align__(256) unsigned char static_scratch[STATIC_SCRATCH_BYTES];
+
+// device address of static_scratch on the current device (looked up once per device)
+static int static_scratch_address(void **out) {
+    constexpr int MAX_DEVICES = 64;
+    static void *cached[MAX_DEVICES] = {nullptr};
+    int dev = 0;
+    GRWS_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= MAX_DEVICES) return fail(GRWS_ERR_UNSUPPORTED, "device ordinal %d beyond %d", dev, MAX_DEVICES);
+    void *p = __atomic_load_n(&cached[dev], __ATOMIC_ACQUIRE);
+    if (p == nullptr) {
+        GRWS_CUDA_TRY(cudaGetSymbolAddress(&p, static_scratch));
+        if (p == nullptr) return fail(GRWS_ERR_CUDA, "cudaGetSymbolAddress returned a null address");
+        __atomic_store_n(&cached[dev], p, __ATOMIC_RELEASE);      // every thread resolves the same address
+    }
+    *out = p;
+    return GRWS_OK;
+}
+
+}  // namespace tc5
+}  // namespace grws
+
+extern "C" __attribute__((visibility("default")))
+int grws_spmm_fwd_static(const int64_t *window_offset, const int32_t *cols, const void *vals, int val_dtype,
+                         const void *B, int b_dtype, int64_t ldb, void *C, int c_dtype, int64_t ldc,
+                         int64_t num_windows, int64_t num_tiles_bound, int64_t K, int64_t N, void *stream) {
+    using namespace grws;
+    GRWS_REQUIRE(num_windows >= 0 && num_tiles_bound >= 0 && K >= 0 && N > 0, "negative size");
+    if (num_windows == 0) return GRWS_OK;
+    GRWS_REQUIRE(window_offset && C && (num_tiles_bound == 0 || (cols && vals && B)), "null pointer");
+    GRWS_REQUIRE(c_dtype >= GRWS_F32 && c_dtype <= GRWS_BF16, "bad output dtype %d", c_dtype);
+    if (val_dtype != b_dtype || !(val_dtype == GRWS_F16 || val_dtype == GRWS_BF16) || !(N == 128 || N == 256))
+        return fail(GRWS_ERR_UNSUPPORTED,
+                    "the allocation-free SpMM covers fp16/bf16 operands with N = 128 or 256 (got dtypes %d/%d, N = %lld); "
+                    "other shapes need grws_spmm_fwd with caller scratch", val_dtype, b_dtype, (long long)N);
+    GRWS_REQUIRE(ldb >= N && ldc >= N, "leading dimension smaller than N");
+    GRWS_REQUIRE((ldb * 2) % 16 == 0 && (ldc * dtype_bytes(c_dtype)) % 16 == 0, "rows of B and C must be 16-byte aligned");
+    GRWS_REQUIRE(aligned16(B) && aligned16(C) && aligned16(vals) && aligned16(cols), "B, C, values and column ids must be 16-byte aligned");
+    const size_t need = spmm_tc5_scratch_bytes(num_tiles_bound, N);
+    if (need > tc5::STATIC_SCRATCH_BYTES)
+        return fail(GRWS_ERR_SCRATCH, "this device needs %zu bytes of SpMM scratch, the built-in array holds %zu "
+                    "(more than %d SMs?); use grws_spmm_fwd with caller scratch", need, tc5::STATIC_SCRATCH_BYTES, tc5::STATIC_MAX_SMS);
+    void *scratch = nullptr;
+    if (int st = tc5::static_scratch_address(&scratch)) return st;
+    return spmm_tc5_launch(window_offset, cols, vals, val_dtype, B, ldb, C, c_dtype, ldc, num_windows, num_tiles_bound,
+                           K, N, scratch, tc5::STATIC_SCRATCH_BYTES, static_cast<cudaStream_t>(stream));
+}

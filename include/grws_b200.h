@@ -81,6 +81,32 @@ int grws_spmm_fwd(const int64_t *window_offset, const int32_t *cols, const void 
                   void *scratch, size_t scratch_bytes, int algo, void *stream);
 
 /* ------------------------------------------------------------------------------------------
+ * Forward SpMM that allocates nothing and takes no scratch buffer.  It has no counterpart in
+ * the reference.  It exists for callers that cannot provide device scratch: code that runs
+ * inside another framework's memory pool and only receives its input and output buffers, a
+ * serving loop whose device memory was fixed at start-up, a host that must not call cudaMalloc
+ * at this point.  The kernel's scratch (status word, per-CTA fix-up records, fp32 partial tiles
+ * of windows split between CTAs) lives in a fixed array inside the library instead:
+ *   - GRWS_SPMM_STATIC_SCRATCH_BYTES (about 11 MB) per GPU that loads the library, held until
+ *     the process exits; sized for N <= 256 on devices with up to 160 SMs -- a call that would
+ *     need more returns GRWS_ERR_SCRATCH;
+ *   - covers the tcgen05 kernel only: fp16 / bf16 operands, N = 128 or 256; anything else
+ *     returns GRWS_ERR_UNSUPPORTED (use grws_spmm_fwd with caller scratch);
+ *   - the first call on a device looks up the array's device address (cudaGetSymbolAddress);
+ *     make that first call before any stream capture;
+ *   - every call shares the array, which keeps the previous call's contents (the status word is
+ *     cleared on the stream before each launch).  Calls that overlap on the GPU race on it:
+ *     issue them on one stream, or otherwise order them.
+ * Arguments as grws_spmm_fwd, without scratch and algo.
+ * ------------------------------------------------------------------------------------------ */
+#define GRWS_SPMM_STATIC_SCRATCH_BYTES (256 + 65536 + 16384 + 160 * 2 * 2 * 16 * 256 * 4)
+
+int grws_spmm_fwd_static(const int64_t *window_offset, const int32_t *cols, const void *vals,
+                         int val_dtype, const void *B, int b_dtype, int64_t ldb, void *C,
+                         int c_dtype, int64_t ldc, int64_t num_windows, int64_t num_tiles_bound,
+                         int64_t K, int64_t N, void *stream);
+
+/* ------------------------------------------------------------------------------------------
  * CSR -> BCSR on the device, two phases so that the caller can allocate exact outputs.
  * Replaces csr_to_bcsr_cpu (core/wrapper/convert_wrapper.cpp:27-180; called from
  * data/bcsr.py:209-216) and produces bit-identical arrays: per window the sorted unique
