@@ -154,12 +154,11 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    sampler = ClockSampler(local_rank)
+    sampler.start()
     for _ in range(max(args.warmup, 3)):
         step()
     barrier()
-
-    sampler = ClockSampler(local_rank)
-    sampler.start()
     # ---- timed region: exactly K steps, device time from CUDA events on the launching stream
     barrier()
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
@@ -169,7 +168,15 @@ def run_ours(args):
         ev[i + 1].record()
     barrier()
     total_ms = ev[0].elapsed_time(ev[-1])
+    # the timed region lasts a few milliseconds, shorter than nvidia-smi's sampling period: keep the
+    # same steps running (untimed) for half a second so that the clock record covers this load
+    t_end = time.perf_counter() + 0.5
+    while time.perf_counter() < t_end:
+        for _ in range(20):
+            step()
+        torch.cuda.synchronize()
     clocks = sampler.stop()
+    clocks["window"] = "warm-up + timed steps + 0.5 s of the same steps, untimed"
 
     # ---- dominant kernel alone (forward product): average launch duration, live
     fwd_ms = []
@@ -217,7 +224,7 @@ def run_ours(args):
 
     cpu_base = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        cpu_base = cpu_baseline(args.workload, csr, H_host, fraction=0.25)
+        cpu_base = cpu_baseline(args.workload, csr, H_host, G_host)
 
     if rank == 0:
         peak, peak_kind = measured_peaks()
@@ -242,7 +249,10 @@ def run_ours(args):
             "roofline": {"bound": "hbm", "kernel": "forward SpMM", "achieved": achieved, "peak": peak,
                          "peak_source": peak_kind, "unit": "GB/s", "frac": achieved / peak,
                          "frac_of_nominal_8TBs": achieved / 8000.0, "launch_ms": fwd_avg_ms,
-                         "algorithmic_bytes": bytes_fwd, "traffic": None},
+                         "algorithmic_bytes": bytes_fwd,
+                         # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu capture
+                         # summarised in profiles/spmm_tc5_kernel_spmm_mid.md (spmm_mid, tcgen05 kernel only)
+                         "traffic": 153.5e6 if (args.workload == "spmm_mid" and args.algo != "warp") else None},
             "e2e": {"value": world * bytes_step / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s",
                     "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": int(H_pin.numel() + G_pin.numel()) * esize,
@@ -257,28 +267,26 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
-def cpu_baseline(workload, csr, H_host, fraction=0.25, repeats=3):
-    """The CPU restatement of the reference path (oracle/, OpenMP) on the first `fraction` of the
-    windows of the same graph; GB/s uses the algorithmic bytes of that sample."""
+def cpu_baseline(workload, csr, H_host, G_host, budget_s=12.0):
+    """The CPU restatement of the reference path (oracle/, OpenMP over all host threads): forward and
+    transposed product of the same workload, repeated until about `budget_s` seconds have passed."""
     import oracle
     from graph_rws_b200.data import synthetic
-    n_rows = int(csr.num_nodes * fraction) // 16 * 16
-    rp = csr.row_ptr[:n_rows + 1]
-    ci, vv = csr.col_idx[:rp[-1]], csr.values[:rp[-1]]
-    wo, cols, vals = oracle.csr_to_bcsr(n_rows, rp, ci, vv)
-    B = H_host.float().numpy()
+    wo, cols, vals = oracle.csr_to_bcsr(csr.num_nodes, csr.row_ptr, csr.col_idx, csr.values)
+    vals = H_host.new_tensor(vals).float().numpy()          # rounded to the storage dtype like the GPU copy
+    B, G = H_host.float().numpy(), G_host.float().numpy()
     esize = H_host.element_size()
-    touched = int(np.unique(ci).size)
-    nbytes = synthetic.spmm_algorithmic_bytes(wo.shape[0] - 1, int(wo[-1]), touched, B.shape[1], esize, esize, esize)
-    best = None
-    for _ in range(repeats):
+    nbytes = 2 * synthetic.spmm_algorithmic_bytes(wo.shape[0] - 1, int(wo[-1]), csr.num_nodes, B.shape[1], esize, esize, esize)
+    times, t_start = [], time.perf_counter()
+    while not times or (time.perf_counter() - t_start < budget_s and len(times) < 50):
         t0 = time.perf_counter()
         oracle.spmm_fwd(wo, cols, vals, B)
-        dt = time.perf_counter() - t0
-        best = dt if best is None else min(best, dt)
+        oracle.spmm_transpose(wo, cols, vals, G, csr.num_nodes)
+        times.append(time.perf_counter() - t0)
+    best = min(times)
     return {"value": nbytes / best / 1e9, "unit": "GB/s", "cores": oracle.num_threads(), "kind": "port",
-            "sample": "forward product over the first %d of %d rows (%d tiles), best of %d, %.3f s"
-                      % (n_rows, csr.num_nodes, int(wo[-1]), repeats, best)}
+            "sample": "whole workload (forward + transposed product), best of %d steps in %.1f s, %.3f s per step"
+                      % (len(times), time.perf_counter() - t_start, best)}
 
 
 def run_reference(args):
@@ -322,7 +330,7 @@ def run_reference(args):
         "scaling": "weak", "vs_baseline": None, "dtype": dt, "data": "synthetic",
         "config": {"workload": args.workload, "nodes": csr.num_nodes, "nnz": csr.nnz, "tiles": T, "width": width},
         "cpu_baseline": {"value": value, "unit": "GB/s", "cores": oracle.num_threads(), "kind": "port",
-                         "sample": "full workload, forward (OpenMP) + transposed (serial) per step"},
+                         "sample": "whole workload, forward + transposed product per step, OpenMP over all host threads"},
         "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }), flush=True)
 

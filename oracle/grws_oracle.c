@@ -167,26 +167,38 @@ API void grws_oracle_spmm_fwd(int64_t W, int64_t N, int64_t tile_rows, int64_t t
 /*   semantics of spmm_bcsr_transpose_atomic_kernel (core/include/spmm_tc.cuh:238-269):        */
 /*   grad_in[col] += A[r,c] * grad_out[row]; -1 columns skipped (:258), zero weights skipped   */
 /*   (:264).  The reference also skips |g| < 1e-9 (:250), which changes the sum by less than   */
-/*   the tolerance; this restatement adds every term, in float64, serially (deterministic).    */
+/*   the tolerance; this restatement adds every term, in float64, in a fixed order.    */
 /* ------------------------------------------------------------------------------------------ */
 API void grws_oracle_spmm_transpose(int64_t W, int64_t F, int64_t tile_rows, int64_t tile_cols,
                                     const int64_t *window_offset, const int32_t *cols,
                                     const float *vals, const float *grad_out, int64_t num_cols,
                                     float *grad_in) {
     double *acc = (double *)calloc((size_t)(num_cols * F), sizeof(double));
-    for (int64_t w = 0; w < W; ++w)
-        for (int64_t t = window_offset[w]; t < window_offset[w + 1]; ++t)
-            for (int64_t r = 0; r < tile_rows; ++r) {
-                const float *g = grad_out + (w * tile_rows + r) * F;
-                for (int64_t c = 0; c < tile_cols; ++c) {
-                    int32_t col = cols[t * tile_cols + c];
-                    if (col == -1) continue;
-                    float a = vals[t * tile_rows * tile_cols + r * tile_cols + c];
-                    if (a == 0.0f) continue;
-                    double *o = acc + (int64_t)col * F;
-                    for (int64_t f = 0; f < F; ++f) o[f] += (double)a * (double)g[f];
-                }
-            }
+    /* threads split the feature range, so every output element is summed by one thread in the
+     * same (window, tile, row, slot) order: parallel and still deterministic */
+#pragma omp parallel
+    {
+#ifdef _OPENMP
+        const int nt = omp_get_num_threads(), tid = omp_get_thread_num();
+#else
+        const int nt = 1, tid = 0;
+#endif
+        const int64_t f0 = F * tid / nt, f1 = F * (tid + 1) / nt;
+        if (f1 > f0)
+            for (int64_t w = 0; w < W; ++w)
+                for (int64_t t = window_offset[w]; t < window_offset[w + 1]; ++t)
+                    for (int64_t r = 0; r < tile_rows; ++r) {
+                        const float *g = grad_out + (w * tile_rows + r) * F;
+                        for (int64_t c = 0; c < tile_cols; ++c) {
+                            int32_t col = cols[t * tile_cols + c];
+                            if (col == -1) continue;
+                            float a = vals[t * tile_rows * tile_cols + r * tile_cols + c];
+                            if (a == 0.0f) continue;
+                            double *o = acc + (int64_t)col * F;
+                            for (int64_t f = f0; f < f1; ++f) o[f] += (double)a * (double)g[f];
+                        }
+                    }
+    }
     for (int64_t i = 0; i < num_cols * F; ++i) grad_in[i] = (float)acc[i];
     free(acc);
 }
