@@ -8,7 +8,8 @@ import ctypes
 import os
 
 _CSRC = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "csrc")
-LIB_PATH = os.path.join(_CSRC, "libgrws_b200.so")
+# GRWS_LIB_PATH selects another build of the same library (kernel-variant comparisons)
+LIB_PATH = os.environ.get("GRWS_LIB_PATH") or os.path.join(_CSRC, "libgrws_b200.so")
 
 c_i64, c_i32, c_sz, c_vp = ctypes.c_int64, ctypes.c_int, ctypes.c_size_t, ctypes.c_void_p
 

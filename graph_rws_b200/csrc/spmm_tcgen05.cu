@@ -32,7 +32,13 @@ namespace grws {
 
 namespace tc5 {
 
-constexpr int STAGE_TILES = 8;                       // tiles per pipeline stage (4 MMA K-steps)
+#ifndef GRWS_TC5_STAGE_TILES
+#define GRWS_TC5_STAGE_TILES 8
+#endif
+#ifndef GRWS_TC5_STAGES
+#define GRWS_TC5_STAGES 4
+#endif
+constexpr int STAGE_TILES = GRWS_TC5_STAGE_TILES;    // tiles per pipeline stage (two per MMA K-step)
 constexpr int STAGE_SLOTS = STAGE_TILES * TILE_COLS; // gathered rows per stage
 constexpr int MMAS_PER_STAGE = STAGE_TILES / 2;
 constexpr int SLAB = 128;                            // features per MMA (its M dimension)
@@ -50,11 +56,15 @@ constexpr int META_TILE_BYTES = STAGE_TILES * TILE_BYTES;
 constexpr int META_COL_BYTES = STAGE_TILES * TILE_COLS * 4;
 constexpr int META_CMD_BYTES = 16;                   // per-stage command word written by the TMA warp
 constexpr int META_BYTES = META_TILE_BYTES + META_COL_BYTES + META_CMD_BYTES;
-// command word: bits 0-3 tile count, bit 4 first stage of a window segment, bit 5 last stage,
-// bit 6 end of this CTA's work
-constexpr uint32_t CMD_FIRST = 1u << 4, CMD_LAST = 1u << 5, CMD_END = 1u << 6;
+// command word: bits 0-4 tile count, bit 8 first stage of a window segment, bit 9 last stage,
+// bit 10 end of this CTA's work
+constexpr uint32_t CMD_COUNT = 31u, CMD_FIRST = 1u << 8, CMD_LAST = 1u << 9, CMD_END = 1u << 10;
+static_assert(STAGE_TILES <= (int)CMD_COUNT && STAGE_TILES % 2 == 0, "tile count field of the command word");
 constexpr int NACC = 4;                              // accumulator buffers in tensor memory
-constexpr int NUM_PRODUCER_WARPS = 8;                 // two per gather slot
+#ifndef GRWS_TC5_PRODUCER_WARPS
+#define GRWS_TC5_PRODUCER_WARPS 8
+#endif
+constexpr int NUM_PRODUCER_WARPS = GRWS_TC5_PRODUCER_WARPS;   // a multiple of the stage count and of four
 constexpr int NUM_EPILOGUE = 128;
 constexpr int EPILOGUE_WARP0 = NUM_PRODUCER_WARPS;       // four warps; warp % 4 is its TMEM lane quarter
 constexpr int MMA_WARP = EPILOGUE_WARP0 + 4;
@@ -251,7 +261,7 @@ struct Walker {
 };
 
 struct SharedStorage {
-    uint64_t full_g[16], empty_g[16], full_m[32], empty_m[32], acc_full[NACC], acc_empty[NACC];
+    uint64_t full_g[16], empty_g[16], full_m[64], empty_m[64], acc_full[NACC], acc_empty[NACC];
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -260,13 +270,14 @@ template <int NH> struct Cfg {
     // two CTAs per SM for one slab (their MMA-issuing threads overlap each other's latency),
     // one CTA per SM for two slabs (a stage is twice as large)
     static constexpr int kCtasPerSm = (NH == 1) ? 2 : 1;
-    static constexpr int kStages = 4;
+    static constexpr int kStages = GRWS_TC5_STAGES;
     // tile / column-id slots: the TMA warp runs kMeta - kStages stages ahead of the data it has
     // already landed, which has to cover the HBM latency of the tile stream
-    static constexpr int kMeta = (NH == 1) ? 16 : 20;
+    static constexpr int kMeta = kStages + ((NH == 1) ? 12 : 16) * 8 / STAGE_TILES;
     static constexpr int kStageBytes = MMAS_PER_STAGE * NH * A_MMA_BYTES;
     static constexpr int kAccCols = 16 * NH;
     static constexpr int kTmemCols = (NACC * kAccCols) < 32 ? 32 : NACC * kAccCols;   // 64 or 128: powers of two
+    static_assert(kStages <= 16 && kMeta <= 64, "barrier arrays in SharedStorage");
     static constexpr size_t kSmem = 1024 + sizeof(SharedStorage) + 16 + (size_t)kStages * kStageBytes + (size_t)kMeta * META_BYTES;
 };
 
@@ -452,16 +463,19 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
         // consecutive slots x 64 features; 16 lanes of each warp cover two of the stage's four
         // K-steps (TMA instructions of different lanes issue one after the other, so the work of a
         // stage is split between two warps).  The copies complete on the stage's barrier.
-        static_assert(NUM_PRODUCER_WARPS == 2 * Cfg<NH>::kStages, "two producer warps per gather slot");
-        static_assert(MMAS_PER_STAGE == 4, "lane mapping assumes four K-steps per stage");
+        constexpr int WARPS_PER_SLOT = NUM_PRODUCER_WARPS / Cfg<NH>::kStages;
+        constexpr int OPS_PER_WARP = MMAS_PER_STAGE * 8 / WARPS_PER_SLOT;      // one copy per lane
+        static_assert(WARPS_PER_SLOT >= 1 && WARPS_PER_SLOT * Cfg<NH>::kStages == NUM_PRODUCER_WARPS, "producer warps per slot");
+        static_assert(OPS_PER_WARP >= 1 && OPS_PER_WARP <= 32 && OPS_PER_WARP * WARPS_PER_SLOT == MMAS_PER_STAGE * 8, "copies per warp");
         const uint64_t keep = policy_keep();
-        const int member = warp & 1;
-        const bool issuer = lane < 16;
-        const int m = 2 * member + ((lane >> 3) & 1), grp = (lane >> 1) & 3, half = lane & 1;
+        const int member = warp % WARPS_PER_SLOT;
+        const bool issuer = lane < OPS_PER_WARP;
+        const int op = member * OPS_PER_WARP + lane;          // (K-step, slot group, feature half) of this lane's copy
+        const int m = op >> 3, grp = (op >> 1) & 3, half = op & 1;
         // slots 4*grp .. 4*grp+3 of K-step m: slot half grp / 2, lines (4*grp) % 8 .. +3 of the atom
         const uint32_t lane_off = (uint32_t)(m * NH * A_MMA_BYTES + (grp >> 1) * A_SBO + half * A_LBO + ((4 * grp) & 7) * 128);
         long long w_full_m = 0, w_empty_g = 0;
-        const uint32_t gs = (uint32_t)(warp >> 1);
+        const uint32_t gs = (uint32_t)(warp / WARPS_PER_SLOT);
         const uint32_t full_bar = smem_u32(&ss->full_g[gs]), empty_bar = smem_u32(&ss->empty_g[gs]);
         const uint32_t dst = smem_u32(ring_g + (size_t)gs * C::kStageBytes) + lane_off;
         uint32_t gph = 0;
@@ -476,7 +490,7 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
             const uint8_t *meta = ring_m + (size_t)ms * META_BYTES;
             const uint32_t cmd = *reinterpret_cast<const volatile uint32_t *>(meta + META_TILE_BYTES + META_COL_BYTES);
             const bool end = (cmd & CMD_END) != 0;
-            const int ntiles = end ? 0 : (int)(cmd & 15u);
+            const int ntiles = end ? 0 : (int)(cmd & CMD_COUNT);
             const int nvalid = ntiles * TILE_COLS;               // slots that carry a column id
             const int nmma = (ntiles + 1) >> 1;
             // the four column ids of this lane's slots (slots past the last tile read nothing)
@@ -523,7 +537,7 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
                 prof_mark<PROF>(prm.dbg, it, 5);
                 const uint32_t cmd = *reinterpret_cast<const volatile uint32_t *>(ring_m + ms * META_BYTES + META_TILE_BYTES + META_COL_BYTES);
                 if (cmd & CMD_END) break;
-                const int nmma = (int)((cmd & 15u) + 1u) >> 1;
+                const int nmma = (int)((cmd & CMD_COUNT) + 1u) >> 1;
                 if (cmd & CMD_FIRST) {
                     buf = ai % NACC;
                     const uint32_t aph = (ai / NACC) & 1u;
