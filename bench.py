@@ -33,6 +33,8 @@ WORKLOADS = {
     "spmm_mid": ("spmm_mid", 128, "f16"),
     "small_gcn": ("small_gcn", 16, "f32"),
 }
+# secondary lines of the metric ("GCN epoch ms", "sampled seeds/s"); not the default
+SECONDARY = ("gcn_small", "sampled")
 
 
 def measured_peaks():
@@ -335,17 +337,118 @@ def run_reference(args):
     }), flush=True)
 
 
+def run_secondary(args):
+    """`gcn_small`: full-batch 2-layer GCN on the 2,708-node graph (fp32, 1,440 padded features,
+    hidden 16, 7 classes), one step = one epoch.  `sampled`: mini-batch training on the
+    2,449,029-node graph shape scaled by --scale (fanouts [15,10,5], 1,024 seeds per GPU per step,
+    3-layer hidden-256 GCN, 100 features, 47 classes), data-parallel with a gradient all-reduce;
+    reports seeds/s for the whole step and for sampling + block build alone."""
+    import torch
+    import torch.distributed as dist
+    from graph_rws_b200 import BCSRGraph, GCN_BCSR
+    from graph_rws_b200.data import synthetic
+    from graph_rws_b200.helper import train_step_full, train_step_sampled
+    from graph_rws_b200.sampler import BCSRSampler
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    torch.manual_seed(1234)
+    extra = {}
+    if args.workload == "gcn_small":
+        csr = synthetic.graph_for_config("small_gcn")
+        graph = BCSRGraph.from_csr(csr.num_nodes, csr.row_ptr, csr.col_idx, csr.values, device=device)
+        x = (torch.rand(csr.num_nodes, 1440, generator=torch.Generator().manual_seed(5)) < 0.013).float()
+        x[:, 1433:] = 0
+        x = x.to(device)
+        y = torch.randint(0, 7, (csr.num_nodes,), generator=torch.Generator().manual_seed(6)).to(device)
+        idx = torch.arange(csr.num_nodes, device=device)
+        model = GCN_BCSR(1440, 16, 7, num_layers=2, dropout=0.5, use_checkpoint=True).to(device)
+        opt = torch.optim.Adam(model.parameters(), lr=0.01)
+        step = lambda: train_step_full(model, graph, x, y, idx, opt)   # noqa: E731
+        metric, unit, hib, units_per_step = "GCN epoch ms (full-batch 2-layer, 2,708 nodes)", "ms", False, None
+        cfg = {"workload": "gcn_small", "nodes": csr.num_nodes, "nnz": csr.nnz, "hidden": 16, "dtype": "f32"}
+    else:
+        csr = synthetic.graph_for_config("sampled_mid", scale=args.scale)
+        graph = BCSRGraph.from_csr(csr.num_nodes, csr.row_ptr, csr.col_idx, csr.values, device=device)
+        x = torch.randn(csr.num_nodes, 100, generator=torch.Generator().manual_seed(7)).half().to(device)
+        y = torch.randint(0, 47, (csr.num_nodes,), generator=torch.Generator().manual_seed(8)).to(device)
+        train = torch.randperm(csr.num_nodes, generator=torch.Generator().manual_seed(9))[:csr.num_nodes // 10]
+        model = GCN_BCSR(100, 256, 47, num_layers=3, dropout=0.5, use_checkpoint=False).to(device).half()
+        opt = torch.optim.Adam(model.parameters(), lr=1e-3, eps=1e-4)
+        sampler = BCSRSampler([15, 10, 5], verbose=False)
+        per_gpu = 1024
+        state = {"i": 0}
+
+        def seeds_for_step():
+            lo = ((state["i"] * world + rank) * per_gpu) % max(train.numel() - per_gpu, 1)
+            state["i"] += 1
+            sampler.step = state["i"]
+            return train[lo:lo + per_gpu].to(device=device, dtype=torch.int32)
+
+        step = lambda: train_step_sampled(model, sampler, graph, x, y, seeds_for_step(), opt)   # noqa: E731
+        metric, unit, hib, units_per_step = "sampled seeds/s (sample + build + 3-layer GCN step)", "seeds/s", True, per_gpu * world
+        cfg = {"workload": "sampled", "scale": args.scale, "nodes": csr.num_nodes, "nnz": csr.nnz,
+               "fanouts": [15, 10, 5], "seeds_per_gpu": per_gpu, "hidden": 256, "dtype": "f16"}
+        # sampling + dedup + block build alone
+        for _ in range(3):
+            sampler.sample_layers(graph, seeds_for_step())
+        barrier()
+        t0 = time.perf_counter()
+        n_s = 20
+        for _ in range(n_s):
+            sampler.sample_layers(graph, seeds_for_step())
+        barrier()
+        extra["sampling_only_seeds_per_s"] = world * per_gpu * n_s / (time.perf_counter() - t0)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    ms = torch.tensor([e0.elapsed_time(e1) / args.steps], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms = float(ms)
+    if rank == 0:
+        value = ms if units_per_step is None else units_per_step / (ms * 1e-3)
+        line = {"metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps,
+                "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": hib, "scaling": "weak",
+                "vs_baseline": None, "dtype": cfg["dtype"], "data": "synthetic", "config": cfg}
+        line.update(extra)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="spmm_mid", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="spmm_mid", choices=sorted(WORKLOADS) + list(SECONDARY))
+    ap.add_argument("--scale", type=float, default=0.1, help="node/edge scale of the `sampled` workload")
     ap.add_argument("--algo", default="auto", choices=["auto", "warp", "tcgen05"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.workload in SECONDARY:
+        run_secondary(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

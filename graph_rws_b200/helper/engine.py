@@ -1,0 +1,59 @@
+"""Minimal training steps: the callers that turn kernel throughput into "epoch ms" and "seeds/s".
+
+Restates, for the two modes the hot path serves, the reference's ``train_epoch_full``
+(helper/engine.py:44-83) and the consumer half of ``train_epoch_node_sampling``
+(helper/engine.py:156-201): forward, cross-entropy on the training rows, backward, gradient-norm
+clipping at 1.0, optimizer step.  With per-node sampled blocks the seed -> logit-row mapping of
+helper/engine.py:175-183 (a searchsorted over ``active_windows``) becomes the identity on the first
+``len(seeds)`` rows.  Data-parallel ranks all-reduce the gradients (NCCL) before the step.
+"""
+import torch
+import torch.distributed as dist
+import torch.nn.functional as F
+
+
+def _allreduce_grads(model, group=None):
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size(group) == 1:
+        return
+    grads = [p.grad for p in model.parameters() if p.grad is not None]
+    if not grads:
+        return
+    flat = torch.cat([g.reshape(-1) for g in grads])
+    dist.all_reduce(flat, group=group)
+    flat /= dist.get_world_size(group)
+    off = 0
+    for g in grads:
+        g.copy_(flat[off:off + g.numel()].view_as(g))
+        off += g.numel()
+
+
+def train_step_full(model, graph, features, labels, train_idx, optimizer):
+    """One full-graph epoch (= one step); returns the loss tensor (no host sync)."""
+    model.train()
+    optimizer.zero_grad(set_to_none=True)
+    logits = model(graph, features)
+    loss = F.cross_entropy(logits[train_idx].float(), labels[train_idx])
+    loss.backward()
+    _allreduce_grads(model)
+    torch.nn.utils.clip_grad_norm_(model.parameters(), max_norm=1.0)
+    optimizer.step()
+    return loss.detach()
+
+
+def train_step_sampled(model, sampler, graph, features, labels, seeds, optimizer, fetch_rows=None):
+    """One mini-batch step: sample the blocks for ``seeds``, gather the input rows, train.
+
+    ``fetch_rows(node_ids)`` supplies feature rows when they are sharded across ranks
+    (parallel.exchange_rows); by default they are indexed from the local ``features``."""
+    model.train()
+    blocks = sampler.sample_layers(graph, seeds)
+    ids = blocks[0].input_nodes
+    x = fetch_rows(ids) if fetch_rows is not None else features[ids.long()]
+    optimizer.zero_grad(set_to_none=True)
+    logits = model(blocks, x)[:seeds.numel()]
+    loss = F.cross_entropy(logits.float(), labels[seeds.long()])
+    loss.backward()
+    _allreduce_grads(model)
+    torch.nn.utils.clip_grad_norm_(model.parameters(), max_norm=1.0)
+    optimizer.step()
+    return loss.detach()
