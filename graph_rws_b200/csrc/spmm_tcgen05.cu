@@ -20,8 +20,8 @@
 // so power-law window lengths do not matter); a window cut by a range boundary is finished by the
 // fix-up kernel from fp32 partial tiles in scratch, in a fixed order.
 //
-// Warp roles: 0-7 gather producers (two per pipeline stage), 8-11 epilogue (TMEM -> registers ->
-// global), 12 MMA issuer, 13 TMA producer for tile values and column ids.  Every mbarrier wait is bounded: on time-out the
+// Warp roles: 0-3 epilogue (TMEM -> registers -> global), 4 MMA issuer, 5 TMA producer for tile
+// values and column ids, 6.. gather producers (two per pipeline stage).  Every mbarrier wait is bounded: on time-out the
 // kernel raises the status word at the start of scratch and all roles drain and return.
 #include <cuda.h>      // CUtensorMap and the cuTensorMapEncodeTiled prototype (resolved at run time)
 #include <stdlib.h>
@@ -64,12 +64,13 @@ constexpr int NACC = 4;                              // accumulator buffers in t
 #ifndef GRWS_TC5_PRODUCER_WARPS
 #define GRWS_TC5_PRODUCER_WARPS 8
 #endif
-constexpr int NUM_PRODUCER_WARPS = GRWS_TC5_PRODUCER_WARPS;   // a multiple of the stage count and of four
+constexpr int NUM_PRODUCER_WARPS = GRWS_TC5_PRODUCER_WARPS;   // a multiple of the stage count
 constexpr int NUM_EPILOGUE = 128;
-constexpr int EPILOGUE_WARP0 = NUM_PRODUCER_WARPS;       // four warps; warp % 4 is its TMEM lane quarter
+constexpr int EPILOGUE_WARP0 = 0;                        // four warps; warp % 4 is its TMEM lane quarter
 constexpr int MMA_WARP = EPILOGUE_WARP0 + 4;
 constexpr int TMA_WARP = MMA_WARP + 1;
-constexpr int NUM_THREADS = (TMA_WARP + 1) * 32;
+constexpr int PRODUCER_WARP0 = TMA_WARP + 1;
+constexpr int NUM_THREADS = (PRODUCER_WARP0 + NUM_PRODUCER_WARPS) * 32;
 static_assert(EPILOGUE_WARP0 % 4 == 0, "epilogue warps must start at a multiple of four");
 constexpr long long WAIT_LIMIT_CYCLES = 3000000000ll; // a wait gives up after about 1.5-2.5 s of SM clocks
 
@@ -119,6 +120,9 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     long long t0 = 0;
     for (uint32_t i = 0;; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
+#ifdef GRWS_TC5_BACKOFF
+        __nanosleep(GRWS_TC5_BACKOFF);
+#endif
         if ((i & 63u) == 63u) {
             if (*abort_flag) return false;
             const long long now = clock64();
@@ -141,7 +145,7 @@ __device__ __forceinline__ bool mbar_wait_t(uint32_t bar, uint32_t parity, volat
 }
 // timeline of the first stages of CTA 0 (profiling build): event e of stage `it`
 template <bool PROF> __device__ __forceinline__ void prof_mark(long long *dbg, uint32_t it, int e) {
-    if constexpr (PROF) { if (dbg && blockIdx.x == 0 && it < 64) dbg[6144 + it * 8 + e] = clock64(); }
+    if constexpr (PROF) { if (dbg && blockIdx.x == 0 && it < 64) dbg[12288 + it * 8 + e] = clock64(); }
 }
 template <bool PROF> __device__ __forceinline__ long long prof_clock() {
     if constexpr (PROF) return clock64(); else return 0;
@@ -269,7 +273,10 @@ struct SharedStorage {
 template <int NH> struct Cfg {
     // two CTAs per SM for one slab (their MMA-issuing threads overlap each other's latency),
     // one CTA per SM for two slabs (a stage is twice as large)
-    static constexpr int kCtasPerSm = (NH == 1) ? 2 : 1;
+#ifndef GRWS_TC5_CTAS_PER_SM
+#define GRWS_TC5_CTAS_PER_SM 2
+#endif
+    static constexpr int kCtasPerSm = (NH == 1) ? GRWS_TC5_CTAS_PER_SM : 1;
     static constexpr int kStages = GRWS_TC5_STAGES;
     // tile / column-id slots: the TMA warp runs kMeta - kStages stages ahead of the data it has
     // already landed, which has to cover the HBM latency of the tile stream
@@ -316,7 +323,7 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
     const uint32_t tmem_base = ss->tmem_base;
     volatile int *abort_flag = &ss->abort_flag;
 
-    if (warp == TMA_WARP || warp >= EPILOGUE_WARP0 && warp < MMA_WARP) {
+    if (warp == TMA_WARP || (warp >= EPILOGUE_WARP0 && warp < MMA_WARP)) {
         // ---- the two roles that walk the window structure: this CTA's tile range [s, e)
         const int64_t T = __ldg(prm.window_offset + W);
         const int64_t G = gridDim.x;
@@ -455,7 +462,7 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
             }
             if (PROF && prm.dbg && threadIdx.x == EPILOGUE_WARP0 * 32) prm.dbg[blockIdx.x * 16 + 7] = w_af;
         }
-    } else if (warp < NUM_PRODUCER_WARPS) {
+    } else if (warp >= PRODUCER_WARP0) {
         // ------------------------------------------------------------------ gather producers
         // Two warps per pipeline stage: producer warps 2w and 2w+1 own gather slot w and fill every
         // kStages-th stage, so the barrier polls and column-id reads of kStages stages overlap.
@@ -468,14 +475,15 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
         static_assert(WARPS_PER_SLOT >= 1 && WARPS_PER_SLOT * Cfg<NH>::kStages == NUM_PRODUCER_WARPS, "producer warps per slot");
         static_assert(OPS_PER_WARP >= 1 && OPS_PER_WARP <= 32 && OPS_PER_WARP * WARPS_PER_SLOT == MMAS_PER_STAGE * 8, "copies per warp");
         const uint64_t keep = policy_keep();
-        const int member = warp % WARPS_PER_SLOT;
+        const int pwarp = warp - PRODUCER_WARP0;
+        const int member = pwarp % WARPS_PER_SLOT;
         const bool issuer = lane < OPS_PER_WARP;
         const int op = member * OPS_PER_WARP + lane;          // (K-step, slot group, feature half) of this lane's copy
         const int m = op >> 3, grp = (op >> 1) & 3, half = op & 1;
         // slots 4*grp .. 4*grp+3 of K-step m: slot half grp / 2, lines (4*grp) % 8 .. +3 of the atom
         const uint32_t lane_off = (uint32_t)(m * NH * A_MMA_BYTES + (grp >> 1) * A_SBO + half * A_LBO + ((4 * grp) & 7) * 128);
         long long w_full_m = 0, w_empty_g = 0;
-        const uint32_t gs = (uint32_t)(warp / WARPS_PER_SLOT);
+        const uint32_t gs = (uint32_t)(pwarp / WARPS_PER_SLOT);
         const uint32_t full_bar = smem_u32(&ss->full_g[gs]), empty_bar = smem_u32(&ss->empty_g[gs]);
         const uint32_t dst = smem_u32(ring_g + (size_t)gs * C::kStageBytes) + lane_off;
         uint32_t gph = 0;
@@ -517,7 +525,7 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
             }
             if (lane == 0) prof_mark<PROF>(prm.dbg, it, 3);
         }
-        if (PROF && prm.dbg && threadIdx.x == 0) { prm.dbg[blockIdx.x * 16 + 2] = w_full_m; prm.dbg[blockIdx.x * 16 + 3] = w_empty_g; }
+        if (PROF && prm.dbg && threadIdx.x == PRODUCER_WARP0 * 32) { prm.dbg[blockIdx.x * 16 + 2] = w_full_m; prm.dbg[blockIdx.x * 16 + 3] = w_empty_g; }
     } else if (warp == MMA_WARP) {
         // ------------------------------------------------------------------ MMA issuer (one thread)
         if (lane == 0) {
@@ -627,8 +635,8 @@ static int grid_size() {
 }
 
 constexpr size_t STATUS_BYTES = 256;
-constexpr size_t DEBUG_BYTES = 512 * 16 * sizeof(long long);
-constexpr size_t FIX_BYTES = 512 * 4 * sizeof(int64_t);      // per-CTA fix-up records   // per-CTA wait counters (GRWS_TC5_PROFILE=1)
+constexpr size_t DEBUG_BYTES = 1024 * 16 * sizeof(long long);
+constexpr size_t FIX_BYTES = 1024 * 4 * sizeof(int64_t);      // per-CTA fix-up records   // per-CTA wait counters (GRWS_TC5_PROFILE=1)
 
 static bool profile_waits() {
     static const int v = [] { const char *e = getenv("GRWS_TC5_PROFILE"); return e ? atoi(e) : 0; }();
@@ -686,7 +694,7 @@ bool spmm_tc5_supported(int dtype, int64_t N) {
 
 size_t spmm_tc5_scratch_bytes(int64_t num_tiles_bound, int64_t N) {
     (void)num_tiles_bound;
-    return tc5::STATUS_BYTES + tc5::DEBUG_BYTES + tc5::FIX_BYTES + (size_t)tc5::grid_size() * 2 /* CTAs per SM */ * 2 * TILE_ROWS * (size_t)N * sizeof(float);
+    return tc5::STATUS_BYTES + tc5::DEBUG_BYTES + tc5::FIX_BYTES + (size_t)tc5::grid_size() * 4 /* CTAs per SM, at most */ * 2 * TILE_ROWS * (size_t)N * sizeof(float);
 }
 
 int spmm_tc5_launch(const int64_t *window_offset, const int32_t *cols, const void *vals, int dtype,
@@ -750,7 +758,7 @@ namespace tc5 {
 constexpr int STATIC_MAX_SMS = 160;
 constexpr int STATIC_MAX_N = 256;
 constexpr size_t STATIC_SCRATCH_BYTES =
-    STATUS_BYTES + DEBUG_BYTES + FIX_BYTES + (size_t)STATIC_MAX_SMS * 2 * 2 * TILE_ROWS * STATIC_MAX_N * sizeof(float);
+    STATUS_BYTES + DEBUG_BYTES + FIX_BYTES + (size_t)STATIC_MAX_SMS * 4 * 2 * TILE_ROWS * STATIC_MAX_N * sizeof(float);
 static_assert(STATIC_SCRATCH_BYTES == GRWS_SPMM_STATIC_SCRATCH_BYTES, "the header states the size of the built-in scratch");
 
 static __device__ __align__(256) unsigned char static_scratch[STATIC_SCRATCH_BYTES];

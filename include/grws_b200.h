@@ -87,7 +87,7 @@ int grws_spmm_fwd(const int64_t *window_offset, const int32_t *cols, const void 
  * serving loop whose device memory was fixed at start-up, a host that must not call cudaMalloc
  * at this point.  The kernel's scratch (status word, per-CTA fix-up records, fp32 partial tiles
  * of windows split between CTAs) lives in a fixed array inside the library instead:
- *   - GRWS_SPMM_STATIC_SCRATCH_BYTES (about 11 MB) per GPU that loads the library, held until
+ *   - GRWS_SPMM_STATIC_SCRATCH_BYTES (about 21 MB) per GPU that loads the library, held until
  *     the process exits; sized for N <= 256 on devices with up to 160 SMs -- a call that would
  *     need more returns GRWS_ERR_SCRATCH;
  *   - covers the tcgen05 kernel only: fp16 / bf16 operands, N = 128 or 256; anything else
@@ -99,7 +99,7 @@ int grws_spmm_fwd(const int64_t *window_offset, const int32_t *cols, const void 
  *     issue them on one stream, or otherwise order them.
  * Arguments as grws_spmm_fwd, without scratch and algo.
  * ------------------------------------------------------------------------------------------ */
-#define GRWS_SPMM_STATIC_SCRATCH_BYTES (256 + 65536 + 16384 + 160 * 2 * 2 * 16 * 256 * 4)
+#define GRWS_SPMM_STATIC_SCRATCH_BYTES (256 + 131072 + 32768 + 160 * 4 * 2 * 16 * 256 * 4)
 
 int grws_spmm_fwd_static(const int64_t *window_offset, const int32_t *cols, const void *vals,
                          int val_dtype, const void *B, int b_dtype, int64_t ldb, void *C,
