@@ -386,7 +386,7 @@ def run_secondary(args):
         train = torch.randperm(csr.num_nodes, generator=torch.Generator().manual_seed(9))[:csr.num_nodes // 10]
         model = GCN_BCSR(100, 256, 47, num_layers=3, dropout=0.5, use_checkpoint=False).to(device).half()
         opt = torch.optim.Adam(model.parameters(), lr=1e-3, eps=1e-4)
-        sampler = BCSRSampler([15, 10, 5], verbose=False)
+        sampler = BCSRSampler([15, 10, 5], verbose=False, pad_to=4096)
         per_gpu = 1024
         state = {"i": 0}
 

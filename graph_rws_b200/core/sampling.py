@@ -105,10 +105,14 @@ class SamplingTimingResult:
 
 
 def sample_layers_csr(row_ptr, col_idx, values, seeds, fanouts, seed=DEFAULT_SEED, values_dtype=torch.float32,
-                      timing=False):
+                      timing=False, pad_to=0):
     """Multi-hop sampling over a CSR graph.  ``fanouts`` are consumed in the order given (the caller
     passes them output layer first, like sampler/sampler.py:202-204).  Returns one
-    [window_offset, cols, vals, dst_nodes, src_nodes] list per hop and one timing object per hop."""
+    [window_offset, cols, vals, dst_nodes, src_nodes] list per hop and one timing object per hop.
+
+    ``pad_to`` > 0 rounds every hop's source list up to a multiple of ``pad_to`` with -1 entries
+    (nodes without neighbours that nothing refers to), so that the dense products of the training
+    step see a small set of recurring shapes instead of a new one every step."""
     out, timings = [], []
     dst = seeds.to(torch.int32).contiguous()
     dev = dst.device
@@ -121,6 +125,9 @@ def sample_layers_csr(row_ptr, col_idx, values, seeds, fanouts, seed=DEFAULT_SEE
         marks = []
         src, wo, cols, vals = build_block(dst, nbr, w, values_dtype=values_dtype, _marks=marks)
         t3 = time.perf_counter()
+        if pad_to > 0 and src.numel() % pad_to:
+            pad = pad_to - src.numel() % pad_to
+            src = torch.cat([src, torch.full((pad,), -1, dtype=torch.int32, device=dev)])
         out.append([wo, cols, vals, dst, src])
         timings.append(SamplingTimingResult((t1 - t0) * 1e3, (marks[0] - t1) * 1e3, (t3 - marks[0]) * 1e3))
         dst = src

@@ -47,7 +47,7 @@ def train_step_sampled(model, sampler, graph, features, labels, seeds, optimizer
     (parallel.exchange_rows); by default they are indexed from the local ``features``."""
     model.train()
     blocks = sampler.sample_layers(graph, seeds)
-    ids = blocks[0].input_nodes
+    ids = blocks[0].input_nodes.clamp(min=0)        # padding entries (-1) fetch row 0; nothing refers to them
     x = fetch_rows(ids) if fetch_rows is not None else features[ids.long()]
     optimizer.zero_grad(set_to_none=True)
     logits = model(blocks, x)[:seeds.numel()]

@@ -41,7 +41,8 @@ class BCSRSampler:
                  gamma_bonus: float = 0.0,
                  score_scale: float = 100.0,
                  locality_enabled: bool = False,
-                 seed: int = core.sampling.DEFAULT_SEED):
+                 seed: int = core.sampling.DEFAULT_SEED,
+                 pad_to: int = 0):
         if hacs_enabled or locality_enabled:
             raise ValueError("importance-score sampling is not part of this library; sampling is uniform")
         if tile_rows != 16 or tile_cols != 8:
@@ -54,6 +55,9 @@ class BCSRSampler:
         self.verbose = verbose
         self.time_tracker = {}
         self.seed = int(seed)
+        # > 0: every hop's node list is padded with -1 entries to a multiple of this, so that the
+        # dense products of a training step see recurring shapes (input_nodes then contains -1s)
+        self.pad_to = int(pad_to)
         self.step = 0          # callers may bump this to decorrelate epochs: the stream key is seed + step
 
     @staticmethod
@@ -84,7 +88,8 @@ class BCSRSampler:
         reversed_fanouts = list(reversed(self.fanouts))
         hops, timing_list = core.sample_layers_csr(row_ptr, col_idx, values, seed_nodes, reversed_fanouts,
                                                    seed=self.seed + self.step,
-                                                   values_dtype=g.values_condensed.dtype, timing=self.verbose)
+                                                   values_dtype=g.values_condensed.dtype, timing=self.verbose,
+                                                   pad_to=self.pad_to)
         if self.verbose:
             num_layers = len(self.fanouts)
             for i, t in enumerate(timing_list):

@@ -120,3 +120,27 @@ def test_reference_named_sampling_entry_points(oracle, graph):
     new2 = core.reindex_bcsr(torch.tensor([-1, 3] * 4, dtype=torch.int32, device="cuda"), torch.ones(128, device="cuda"),
                              torch.tensor([0], dtype=torch.int32, device="cuda"))
     assert new2.cpu().tolist() == [-1, 3] * 4
+
+
+def test_padded_hops_keep_the_real_part_identical(graph):
+    """pad_to only appends -1 nodes: the real rows / columns of every block are unchanged."""
+    from graph_rws_b200 import BCSRGraph
+    from graph_rws_b200.sampler import BCSRSampler
+    g = BCSRGraph.from_csr(graph.num_nodes, graph.row_ptr, graph.col_idx, graph.values, device=torch.device("cuda"))
+    seeds = torch.arange(0, 600, 3, dtype=torch.int32)
+    exact = BCSRSampler([4, 3], verbose=False, seed=5).sample_layers(g, seeds)
+    padded = BCSRSampler([4, 3], verbose=False, seed=5, pad_to=512).sample_layers(g, seeds)
+    inner_e, inner_p = exact[1], padded[1]
+    assert inner_p.num_cols % 512 == 0 and inner_p.num_cols >= inner_e.num_cols
+    n = inner_e.num_cols
+    assert torch.equal(inner_p.input_nodes[:n], inner_e.input_nodes) and (inner_p.input_nodes[n:] == -1).all()
+    assert torch.equal(inner_p.original_col_indices, inner_e.original_col_indices)
+    outer_e, outer_p = exact[0], padded[0]
+    assert outer_p.num_rows == inner_p.num_cols
+    te = int(outer_e.window_offset[-1])
+    # the padded rows have no neighbours: same tiles, only more (empty) windows
+    assert int(outer_p.window_offset[-1]) == te
+    # ... and new source nodes are numbered after the (longer, padded) destination list
+    ce = outer_e.original_col_indices[:te * 8]
+    shifted = torch.where(ce >= n, ce + (inner_p.num_cols - n), ce)
+    assert torch.equal(outer_p.original_col_indices[:te * 8], shifted)
