@@ -20,8 +20,8 @@
 // so power-law window lengths do not matter); a window cut by a range boundary is finished by the
 // fix-up kernel from fp32 partial tiles in scratch, in a fixed order.
 //
-// Warp roles: 0-3 epilogue (TMEM -> registers -> global), 4 MMA issuer, 5 TMA producer for tile
-// values and column ids, 6.. gather producers (two per pipeline stage).  Every mbarrier wait is bounded: on time-out the
+// Warp roles: 0-3 epilogue (TMEM -> registers -> global), 4 MMA issuer, 5-6 TMA producers for tile
+// values and column ids (alternating stages), 7.. gather producers (two per pipeline stage).  Every mbarrier wait is bounded: on time-out the
 // kernel raises the status word at the start of scratch and all roles drain and return.
 #include <cuda.h>      // CUtensorMap and the cuTensorMapEncodeTiled prototype (resolved at run time)
 #include <stdlib.h>
@@ -69,7 +69,11 @@ constexpr int NUM_EPILOGUE = 128;
 constexpr int EPILOGUE_WARP0 = 0;                        // four warps; warp % 4 is its TMEM lane quarter
 constexpr int MMA_WARP = EPILOGUE_WARP0 + 4;
 constexpr int TMA_WARP = MMA_WARP + 1;
-constexpr int PRODUCER_WARP0 = TMA_WARP + 1;
+#ifndef GRWS_TC5_META_WARPS
+#define GRWS_TC5_META_WARPS 2
+#endif
+constexpr int NUM_META_WARPS = GRWS_TC5_META_WARPS;     // they take the stages round-robin
+constexpr int PRODUCER_WARP0 = TMA_WARP + NUM_META_WARPS;
 constexpr int NUM_THREADS = (PRODUCER_WARP0 + NUM_PRODUCER_WARPS) * 32;
 static_assert(EPILOGUE_WARP0 % 4 == 0, "epilogue warps must start at a multiple of four");
 constexpr long long WAIT_LIMIT_CYCLES = 3000000000ll; // a wait gives up after about 1.5-2.5 s of SM clocks
@@ -309,7 +313,7 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
     if (threadIdx.x == 0) {
         for (int i = 0; i < C::kStages; ++i) { mbar_init(smem_u32(&ss->full_g[i]), 1); mbar_init(smem_u32(&ss->empty_g[i]), 1); }
         for (int i = 0; i < C::kMeta; ++i) { mbar_init(smem_u32(&ss->full_m[i]), 1); mbar_init(smem_u32(&ss->empty_m[i]), 1); }
-        for (int i = 0; i < NACC; ++i) { mbar_init(smem_u32(&ss->acc_full[i]), 1); mbar_init(smem_u32(&ss->acc_empty[i]), NUM_EPILOGUE); }
+        for (int i = 0; i < NACC; ++i) { mbar_init(smem_u32(&ss->acc_full[i]), 1); mbar_init(smem_u32(&ss->acc_empty[i]), NUM_EPILOGUE / 32); }
         ss->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -323,7 +327,8 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
     const uint32_t tmem_base = ss->tmem_base;
     volatile int *abort_flag = &ss->abort_flag;
 
-    if (warp == TMA_WARP || (warp >= EPILOGUE_WARP0 && warp < MMA_WARP)) {
+    const bool is_meta = warp >= TMA_WARP && warp < TMA_WARP + NUM_META_WARPS;
+    if (is_meta || (warp >= EPILOGUE_WARP0 && warp < MMA_WARP)) {
         // ---- the two roles that walk the window structure: this CTA's tile range [s, e)
         const int64_t T = __ldg(prm.window_offset + W);
         const int64_t G = gridDim.x;
@@ -339,8 +344,9 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
         Walker wk;
         wk.init(prm.window_offset, W, s, e, blockIdx.x == 0 ? 0 : w_first, lane);
 
-        if (warp == TMA_WARP) {
+        if (is_meta) {
             // -------------------------------------------------------------- TMA producer
+            const uint32_t meta_id = (uint32_t)(warp - TMA_WARP);
             // streams tile values and column ids of every stage and tells the other roles, through
             // the command word of the stage, what the stage holds
             const uint64_t pol = policy_stream();
@@ -350,6 +356,7 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
             const long long t_start = prof_clock<PROF>();
             while (ok && wk.next_segment(lane)) {
                 for (int64_t t0 = wk.seg_s; ok && t0 < wk.seg_e; t0 += STAGE_TILES, ++it) {
+                    if (it % NUM_META_WARPS != meta_id) continue;      // another meta warp's stage
                     const uint32_t slot = it % C::kMeta, ph = (it / C::kMeta) & 1u;
                     const int ntiles = (int)min((int64_t)STAGE_TILES, wk.seg_e - t0);
                     if (lane == 0) ok = mbar_wait_t<PROF>(smem_u32(&ss->empty_m[slot]), ph ^ 1u, abort_flag, w_empty_m);
@@ -385,7 +392,7 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
                     ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
                 }
             }
-            if (lane == 0) {                // one end marker per producer warp; the MMA warp stops at the first
+            if (lane == 0 && meta_id == 0) {   // one end marker per gather slot; the MMA warp stops at the first
                 for (int j = 0; ok && j < C::kStages; ++j, ++it) {
                     const uint32_t slot = it % C::kMeta, ph = (it / C::kMeta) & 1u;
                     ok = mbar_wait_t<PROF>(smem_u32(&ss->empty_m[slot]), ph ^ 1u, abort_flag, w_empty_m);
@@ -397,7 +404,7 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
                     }
                 }
             }
-            if (PROF && prm.dbg && lane == 0) { prm.dbg[blockIdx.x * 16 + 0] = w_empty_m; prm.dbg[blockIdx.x * 16 + 1] = prof_clock<PROF>() - t_start; }
+            if (PROF && prm.dbg && lane == 0 && meta_id == 0) { prm.dbg[blockIdx.x * 16 + 0] = w_empty_m; prm.dbg[blockIdx.x * 16 + 1] = prof_clock<PROF>() - t_start; }
         } else {
             // -------------------------------------------------------------- epilogue warps
             const uint64_t pol = policy_stream();
@@ -414,16 +421,19 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
                 if (nonempty) {
                     const uint32_t buf = ai % NACC, aph = (ai / NACC) & 1u;
                     ++ai;
-                    ok = mbar_wait_t<PROF>(smem_u32(&ss->acc_full[buf]), aph, abort_flag, w_af);
-                    ok = __all_sync(0xffffffffu, ok) != 0;
-                    if (!ok) { raise(prm, ss, ST_TIMEOUT_ACC); break; }
+                    // one polling lane per warp: threads spinning on a barrier slow every other
+                    // barrier operation of the SM down
+                    if (lane == 0) ok = mbar_wait_t<PROF>(smem_u32(&ss->acc_full[buf]), aph, abort_flag, w_af);
+                    ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+                    if (!ok) { if (lane == 0) raise(prm, ss, ST_TIMEOUT_ACC); break; }
                     tc_fence_after();
 #pragma unroll
                     for (int h = 0; h < NH; ++h)
                         tmem_ld16(tmem_base + ((uint32_t)(32 * q) << 16) + buf * C::kAccCols + h * 16, v[h]);
                     tmem_ld_wait();
                     tc_fence_before();
-                    mbar_arrive(smem_u32(&ss->acc_empty[buf]));
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&ss->acc_empty[buf]));
                 } else {
 #pragma unroll
                     for (int h = 0; h < NH; ++h)
@@ -517,7 +527,10 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
                 break;
             }
             // bytes the K-steps of this stage bring in: 16 slots x 128 features x NH slabs each
-            if (lane == 0 && member == 0) mbar_expect_tx(full_bar, (uint32_t)(nmma * 16 * SLAB * 2 * NH));
+            if (lane == 0 && member == 0) {
+                if (prm.skip & 2) mbar_arrive(full_bar);          // experiment: no gathers, nothing to wait for
+                else mbar_expect_tx(full_bar, (uint32_t)(nmma * 16 * SLAB * 2 * NH));
+            }
             if (issuer && m < nmma && !(prm.skip & 2)) {
 #pragma unroll
                 for (int h = 0; h < NH; ++h)
@@ -535,7 +548,7 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
             const uint64_t a_desc0 = smem_desc(smem_u32(ring_g), A_LBO, A_SBO, 2);
             const uint64_t b_desc0 = smem_desc(smem_u32(ring_m), TILE_BYTES, 128, 0);
             uint32_t ai = 0, buf = 0;
-            long long w_acc = 0, w_fm = 0, w_fg = 0, t_issue = 0, t_commit = 0;
+            long long w_acc = 0, w_fm = 0, w_fg = 0, t_issue = 0, t_commit = 0, t_cmd = 0, t_fence = 0;
             const long long t_mark = prof_clock<PROF>();
             uint32_t it = 0, gs = 0, gph = 0, ms = 0;
             for (;; ++it) {
@@ -543,8 +556,10 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
                 // so this one wait also covers the tile values and the command word.
                 if (!mbar_wait_t<PROF>(smem_u32(&ss->full_g[gs]), gph, abort_flag, w_fg)) { raise(prm, ss, ST_TIMEOUT_FULL); break; }
                 prof_mark<PROF>(prm.dbg, it, 5);
+                const long long tc0 = prof_clock<PROF>();
                 const uint32_t cmd = *reinterpret_cast<const volatile uint32_t *>(ring_m + ms * META_BYTES + META_TILE_BYTES + META_COL_BYTES);
                 if (cmd & CMD_END) break;
+                if (PROF) t_cmd += prof_clock<PROF>() - tc0 + (long long)(cmd & 0);
                 const int nmma = (int)((cmd & CMD_COUNT) + 1u) >> 1;
                 if (cmd & CMD_FIRST) {
                     buf = ai % NACC;
@@ -555,8 +570,10 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
                 // cp.async data is handed over by the mbarrier the producers arrive on after their
                 // copies have landed; no generic->async proxy fence is issued here (it would also
                 // wait for every younger gather in flight)
+                const long long tf0 = prof_clock<PROF>();
                 tc_fence_after();
                 const long long ti0 = prof_clock<PROF>();
+                t_fence += ti0 - tf0;
                 const uint32_t d_tmem = tmem_base + buf * C::kAccCols;
                 const uint64_t ad = a_desc0 + (uint64_t)(gs * (C::kStageBytes >> 4));
                 const uint64_t bd = b_desc0 + (uint64_t)(ms * (META_BYTES >> 4));
@@ -582,7 +599,7 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
             }
             if (PROF && prm.dbg) {
                 long long *d = prm.dbg + blockIdx.x * 16;
-                d[4] = w_acc; d[5] = w_fm; d[6] = w_fg; d[8] = t_issue; d[9] = t_commit; d[10] = prof_clock<PROF>() - t_mark; d[11] = it;
+                d[4] = w_acc; d[5] = w_fm; d[6] = w_fg; d[8] = t_issue; d[9] = t_commit; d[10] = prof_clock<PROF>() - t_mark; d[11] = it; d[12] = t_cmd; d[13] = t_fence;
             }
         }
         __syncwarp();
