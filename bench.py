@@ -34,7 +34,7 @@ WORKLOADS = {
     "small_gcn": ("small_gcn", 16, "f32"),
 }
 # secondary lines of the metric ("GCN epoch ms", "sampled seeds/s"); not the default
-SECONDARY = ("gcn_small", "sampled")
+SECONDARY = ("gcn_small", "gcn_full", "sampled")
 
 
 def measured_peaks():
@@ -342,7 +342,11 @@ def run_secondary(args):
     hidden 16, 7 classes), one step = one epoch.  `sampled`: mini-batch training on the
     2,449,029-node graph shape scaled by --scale (fanouts [15,10,5], 1,024 seeds per GPU per step,
     3-layer hidden-256 GCN, 100 features, 47 classes), data-parallel with a gradient all-reduce;
-    reports seeds/s for the whole step and for sampling + block build alone."""
+    reports seeds/s for the whole step and for sampling + block build alone.  `gcn_full`:
+    full-graph 2-layer GCN on the 232,965-node, 114.6 M-nnz dense-community shape scaled by --scale
+    (nodes x scale, nnz x scale^2; bf16, 602 features padded to 608, hidden 256, 41 classes); with
+    N > 1 ranks the windows are row-partitioned by tile count and H (forward) / dY (backward) are
+    all-gathered per layer, total work fixed (strong scaling)."""
     import torch
     import torch.distributed as dist
     from graph_rws_b200 import BCSRGraph, GCN_BCSR
@@ -378,6 +382,46 @@ def run_secondary(args):
         step = lambda: train_step_full(model, graph, x, y, idx, opt)   # noqa: E731
         metric, unit, hib, units_per_step = "GCN epoch ms (full-batch 2-layer, 2,708 nodes)", "ms", False, None
         cfg = {"workload": "gcn_small", "nodes": csr.num_nodes, "nnz": csr.nnz, "hidden": 16, "dtype": "f32"}
+    elif args.workload == "gcn_full":
+        from graph_rws_b200.helper import train_step_full_sharded
+        from graph_rws_b200.parallel import RowShardedGraph, partition_windows_by_tiles
+        sc = args.scale
+        n = int(232965 * sc)
+        e = int((114_600_000 * sc * sc - n) // 2)
+        rp, ci, vv = synthetic.community_csr_torch(n, e, 50, 0.8, 1003, device)
+        if world > 1:      # every rank draws the graph itself: the draws must agree
+            chk = torch.stack([ci.long().sum(), -ci.long().sum()])
+            dist.all_reduce(chk, op=dist.ReduceOp.MAX)
+            assert int(chk[0]) == -int(chk[1]), "ranks drew different graphs"
+        nnz = int(ci.numel())
+        graph = BCSRGraph.from_csr(n, rp, ci, vv, device=device, values_dtype=torch.bfloat16)
+        del rp, ci, vv
+        gen = torch.Generator(device=device).manual_seed(11)
+        x = torch.randn(n, 608, generator=gen, device=device, dtype=torch.float32).bfloat16()
+        x[:, 602:] = 0
+        y = torch.randint(0, 41, (n,), generator=gen, device=device)
+        train = torch.randperm(n, generator=gen, device=device)[:n // 2].sort().values
+        model = GCN_BCSR(608, 256, 41, num_layers=2, dropout=0.5, use_checkpoint=False).to(device).bfloat16()
+        opt = torch.optim.Adam(model.parameters(), lr=1e-3, eps=1e-4)
+        tiles = int(graph.window_offset[-1])
+        if world == 1:
+            graph.transposed(n, dtype=torch.bfloat16)
+            step = lambda: train_step_full(model, graph, x, y, train, opt)   # noqa: E731
+        else:
+            for p_ in model.parameters():
+                dist.broadcast(p_.data, 0)
+            part = partition_windows_by_tiles(graph.window_offset, world, num_rows=n)
+            lo, hi = part.rows(rank)
+            shard = RowShardedGraph.from_full(graph, part, rank, dtype=torch.bfloat16)
+            x_l, y_l = x[lo:hi].contiguous(), y[lo:hi].contiguous()
+            mine = (train[(train >= lo) & (train < hi)] - lo).contiguous()
+            n_train = train.numel()
+            del graph, x, y
+            torch.cuda.empty_cache()
+            step = lambda: train_step_full_sharded(model, shard, x_l, y_l, mine, n_train, opt)   # noqa: E731
+        metric, unit, hib, units_per_step = "GCN epoch ms (full-graph 2-layer, dense-community graph, row-partitioned)", "ms", False, None
+        cfg = {"workload": "gcn_full", "scale": sc, "nodes": n, "nnz": nnz, "tiles": tiles, "features": 602,
+               "hidden": 256, "classes": 41, "dtype": "bf16", "parallelism": "rows x%d, all-gather of H per layer" % world}
     else:
         csr = synthetic.graph_for_config("sampled_mid", scale=args.scale)
         graph = BCSRGraph.from_csr(csr.num_nodes, csr.row_ptr, csr.col_idx, csr.values, device=device)
@@ -427,7 +471,8 @@ def run_secondary(args):
     if rank == 0:
         value = ms if units_per_step is None else units_per_step / (ms * 1e-3)
         line = {"metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps,
-                "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": hib, "scaling": "weak",
+                "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": hib,
+                "scaling": "strong" if args.workload == "gcn_full" else "weak",
                 "vs_baseline": None, "dtype": cfg["dtype"], "data": "synthetic", "config": cfg}
         line.update(extra)
         print(json.dumps(line), flush=True)
@@ -442,7 +487,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="spmm_mid", choices=sorted(WORKLOADS) + list(SECONDARY))
-    ap.add_argument("--scale", type=float, default=0.1, help="node/edge scale of the `sampled` workload")
+    ap.add_argument("--scale", type=float, default=0.1, help="node/edge scale of the `sampled` and `gcn_full` workloads")
     ap.add_argument("--algo", default="auto", choices=["auto", "warp", "tcgen05"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()

@@ -12,7 +12,7 @@ import torch.distributed as dist
 import torch.nn.functional as F
 
 
-def _allreduce_grads(model, group=None):
+def _allreduce_grads(model, group=None, average=True):
     if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size(group) == 1:
         return
     grads = [p.grad for p in model.parameters() if p.grad is not None]
@@ -20,7 +20,8 @@ def _allreduce_grads(model, group=None):
         return
     flat = torch.cat([g.reshape(-1) for g in grads])
     dist.all_reduce(flat, group=group)
-    flat /= dist.get_world_size(group)
+    if average:
+        flat /= dist.get_world_size(group)
     off = 0
     for g in grads:
         g.copy_(flat[off:off + g.numel()].view_as(g))
@@ -35,6 +36,21 @@ def train_step_full(model, graph, features, labels, train_idx, optimizer):
     loss = F.cross_entropy(logits[train_idx].float(), labels[train_idx])
     loss.backward()
     _allreduce_grads(model)
+    torch.nn.utils.clip_grad_norm_(model.parameters(), max_norm=1.0)
+    optimizer.step()
+    return loss.detach()
+
+
+def train_step_full_sharded(model, graph, features_local, labels_local, train_idx_local, num_train, optimizer):
+    """One full-graph epoch with the rows of the graph, features and labels sharded over the ranks
+    (``graph`` is a parallel.RowShardedGraph).  The loss is the global mean over ``num_train``
+    training rows: every rank sums its own rows' terms, so the weight gradients ADD across ranks."""
+    model.train()
+    optimizer.zero_grad(set_to_none=True)
+    logits = model(graph, features_local)
+    loss = F.cross_entropy(logits[train_idx_local].float(), labels_local[train_idx_local], reduction='sum') / num_train
+    loss.backward()
+    _allreduce_grads(model, average=False)
     torch.nn.utils.clip_grad_norm_(model.parameters(), max_norm=1.0)
     optimizer.step()
     return loss.detach()

@@ -16,7 +16,13 @@ from ..helper import record_spmm_time
 
 
 def _spmm_graph(graph, dense):
-    """A @ dense for a BCSRGraph, values cast (and cached) to the dense dtype, N padded to 8."""
+    """A @ dense for a BCSRGraph, values cast (and cached) to the dense dtype, N padded to 8.
+
+    A graph may bring its own product through a ``gather_dense`` hook: a row-sharded graph
+    (parallel.RowShardedGraph) all-gathers the row shards of ``dense`` before its local product."""
+    gather = getattr(graph, 'gather_dense', None)
+    if gather is not None:
+        dense = gather(dense)
     dense = dense.contiguous()
     vals = graph.values_as(dense.dtype)
     n = dense.shape[1]
@@ -31,7 +37,7 @@ class BCSRSPMMFunction(Function):
     @staticmethod
     def forward(ctx, graph, features, weight, warps_per_block):
         x_mult_w = torch.matmul(features, weight)
-        if core._timing_enabled:
+        if core._timing_enabled and not hasattr(graph, 'gather_dense'):
             output, timing = core.spmm_tc(graph.window_offset, graph.original_col_indices,
                                           graph.values_as(x_mult_w.dtype), x_mult_w.contiguous(),
                                           warps_per_block)

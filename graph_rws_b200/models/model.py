@@ -10,6 +10,8 @@ Graph handling per layer follows models/model.py:96-210:
     (models/model.py:118-125); here the result is remembered per graph and feature count;
   * layers > 0 whose previous graph carries ``active_windows`` get their column ids localised by
     ``reindex_bcsr``;
+  * a row shard of a full graph (parallel.RowShardedGraph) keeps its global column ids; the
+    layer all-gathers the feature rows of all ranks before the product;
   * the rows fed to the self path are gathered by window when ``active_windows`` exist, else the
     target-first slice ``h[:target_rows]`` (what per-seed sampled blocks use).
 """
@@ -65,7 +67,7 @@ class GCN_BCSR(nn.Module):
             norm.reset_parameters()
 
     def _ensure_graph_list(self, graphs: Union[BCSRGraph, List[BCSRGraph]]) -> List[BCSRGraph]:
-        if isinstance(graphs, BCSRGraph):
+        if isinstance(graphs, BCSRGraph) or hasattr(graphs, 'gather_dense'):
             # independent wrappers so that per-layer metadata edits do not leak between layers
             return [copy.copy(graphs) for _ in range(len(self.layers))]
         if isinstance(graphs, list):
@@ -89,6 +91,8 @@ class GCN_BCSR(nn.Module):
             shared[key] = state
 
     def _sanitize_and_reindex(self, layer_idx, curr_g, prev_g, h_in_shape):
+        if hasattr(curr_g, 'gather_dense'):
+            return          # row shard of a square graph: global column ids, rows gathered before the product
         if getattr(curr_g, 'is_local_input', False):
             curr_g.num_cols = h_in_shape[0]
             return

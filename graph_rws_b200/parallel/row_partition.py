@@ -96,3 +96,49 @@ class DistributedSpMM:
         out = core.spmm_raw(g.window_offset, g.original_col_indices, g.values_as(h_full.dtype), h_full.contiguous())
         lo, hi = self.part.rows(self.rank)
         return out[:hi - lo]
+
+
+class RowShardedGraph:
+    """This rank's rows of a square adjacency, usable wherever the layers take a ``BCSRGraph``.
+
+    Forward: the row shards of the dense operand are all-gathered, then the local windows are
+    multiplied.  Backward: ``transposed()`` returns the rank's rows of A^T with the same hook, so
+    ``A^T @ G`` all-gathers the row shards of G and multiplies the local rows of A^T -- no
+    reduce-scatter and no atomics.  Weight gradients are all-reduced by the training step."""
+
+    def __init__(self, local, part: RowPartition, rank: int, local_t=None, group=None):
+        self.local, self.part, self.rank, self.group = local, part, rank, group
+        self._local_t = local_t
+        for name in ("window_offset", "original_col_indices", "values_condensed", "tile_rows", "tile_cols",
+                     "num_windows", "device"):
+            setattr(self, name, getattr(local, name))
+        lo, hi = part.rows(rank)
+        self.num_rows = self.num_nodes = hi - lo
+        self.num_cols = part.num_rows
+        self._shared = local._shared
+
+    @classmethod
+    def from_full(cls, graph, part: RowPartition, rank: int, dtype=None, group=None):
+        """Shard a full graph held by every rank (and its transposed graph) by the same row partition."""
+        from ..data import BCSRGraph
+
+        def shard(g):
+            wo, cols, vals = shard_bcsr(g.window_offset, g.original_col_indices, g.values_condensed, part, rank)
+            lo, hi = part.rows(rank)
+            return BCSRGraph(num_nodes=hi - lo, num_edges=None, tile_rows=16, tile_cols=8, window_offset=wo,
+                             original_col_indices=cols, values_condensed=vals, device=vals.device,
+                             num_rows=hi - lo, num_cols=part.num_rows, values_dtype=vals.dtype)
+        gt = graph.transposed(part.num_rows, dtype=dtype or graph.values_condensed.dtype)
+        return cls(shard(graph), part, rank, local_t=cls(shard(gt), part, rank, group=group), group=group)
+
+    def values_as(self, dtype):
+        return self.local.values_as(dtype)
+
+    def gather_dense(self, dense_local):
+        # a product returns whole windows: rows past the rank's last row are padding
+        return all_gather_rows(dense_local[:self.num_rows], self.part, self.group)
+
+    def transposed(self, num_cols=None, dtype=None):
+        if self._local_t is None:
+            raise RuntimeError("this shard was built without its transposed rows")
+        return self._local_t

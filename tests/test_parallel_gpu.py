@@ -51,17 +51,77 @@ def _worker(rank, world, port, out):
         dist.destroy_process_group()
 
 
-def test_row_partitioned_spmm_and_row_exchange_on_two_gpus():
+def _gcn_worker(rank, world, port, out):
+    """Row-sharded full-graph GCN step == the single-GPU step: loss, logits, weight gradients."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        import torch.nn.functional as F
+        from graph_rws_b200 import BCSRGraph, GCN_BCSR
+        from graph_rws_b200.data import synthetic
+        from graph_rws_b200.helper.engine import _allreduce_grads
+        from graph_rws_b200.parallel import RowShardedGraph, partition_windows_by_tiles
+        n = 7003                                            # last window is partial
+        g = synthetic.sym_normalized_csr(n, *synthetic.chung_lu_edges(n, 90000, 2.2, 5))
+        graph = BCSRGraph.from_csr(g.num_nodes, g.row_ptr, g.col_idx, g.values, device=dev, values_dtype=torch.float16)
+        gen = torch.Generator().manual_seed(8)
+        X = torch.randn(n, 64, generator=gen).to(dev)
+        y = torch.randint(0, 10, (n,), generator=gen).to(dev)
+        train = torch.randperm(n, generator=gen)[:3000].sort().values.to(dev)
+        torch.manual_seed(3)
+        model = GCN_BCSR(64, 128, 10, 3, dropout=0.0, use_checkpoint=(rank == 0)).to(dev)
+        for p in model.parameters():
+            dist.broadcast(p.data, 0)
+
+        def grads():
+            return torch.cat([p.grad.reshape(-1) for p in model.parameters()]).clone()
+
+        ref_logits = model(graph, X)                     # fp32 features: the TF32 warp-MMA kernel
+        ref_loss = F.cross_entropy(ref_logits[train].float(), y[train])
+        ref_loss.backward()
+        ref_grads = grads()
+        model.zero_grad(set_to_none=True)
+
+        part = partition_windows_by_tiles(graph.window_offset, world, num_rows=n)
+        lo, hi = part.rows(rank)
+        shard = RowShardedGraph.from_full(graph, part, rank)
+        mine = train[(train >= lo) & (train < hi)] - lo
+        logits = model(shard, X[lo:hi].contiguous())
+        assert logits.shape[0] == hi - lo
+        loss = F.cross_entropy(logits[mine].float(), y[lo:hi][mine], reduction='sum') / train.numel()
+        loss.backward()
+        _allreduce_grads(model, average=False)
+        dist.all_reduce(loss)
+        assert (logits.float() - ref_logits[lo:hi].float()).norm() / ref_logits[lo:hi].float().norm() < 5e-3
+        assert abs(float(loss) - float(ref_loss)) < 2e-3 * abs(float(ref_loss))
+        assert (grads() - ref_grads).norm() / ref_grads.norm() < 2e-2
+        torch.cuda.synchronize()
+        out[rank] = 1
+    finally:
+        dist.destroy_process_group()
+
+
+def _run(worker):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     world = 2
     ctx = mp.get_context("spawn")
     out = ctx.Array("i", world)
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, out)) for r in range(world)]
+    procs = [ctx.Process(target=worker, args=(r, world, port, out)) for r in range(world)]
     for p in procs:
         p.start()
     for p in procs:
         p.join(timeout=300)
     assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
     assert list(out) == [1] * world
+
+
+def test_row_partitioned_spmm_and_row_exchange_on_two_gpus():
+    _run(_worker)
+
+
+def test_row_sharded_gcn_step_matches_single_gpu():
+    _run(_gcn_worker)
