@@ -74,8 +74,13 @@ constexpr int TMA_WARP = MMA_WARP + 1;
 #endif
 constexpr int NUM_META_WARPS = GRWS_TC5_META_WARPS;     // they take the stages round-robin
 constexpr int PRODUCER_WARP0 = TMA_WARP + NUM_META_WARPS;
+#ifndef GRWS_TC5_MMA_PHYS_WARP
+#define GRWS_TC5_MMA_PHYS_WARP 4
+#endif
+static_assert(GRWS_TC5_MMA_PHYS_WARP >= 4, "warps 0-3 are the epilogue (their index is their TMEM lane quarter)");
 constexpr int NUM_THREADS = (PRODUCER_WARP0 + NUM_PRODUCER_WARPS) * 32;
 static_assert(EPILOGUE_WARP0 % 4 == 0, "epilogue warps must start at a multiple of four");
+constexpr int64_t SPLIT256_OPERAND_BYTES = 8ll << 20;   // dense operand size above which width 256 runs as two 128-column passes
 constexpr long long WAIT_LIMIT_CYCLES = 3000000000ll; // a wait gives up after about 1.5-2.5 s of SM clocks
 
 enum : int { ST_OK = 0, ST_TIMEOUT_FULL = 1, ST_TIMEOUT_EMPTY = 2, ST_TIMEOUT_ACC = 3, ST_TIMEOUT_META = 4 };
@@ -113,8 +118,14 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 }
 __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
+#ifdef GRWS_TC5_WAIT_HINT_NS
+    // the hint lets the hardware keep the thread suspended for up to that long before it reports failure
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity), "r"((uint32_t)GRWS_TC5_WAIT_HINT_NS) : "memory");
+#else
     asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
                  : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+#endif
     return ok;
 }
 // bounded wait: gives up after WAIT_LIMIT_CYCLES SM clocks or when another role already aborted.
@@ -307,7 +318,10 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
     uint8_t *ring_m = ring_g + (size_t)C::kStages * C::kStageBytes;
     SharedStorage *ss = reinterpret_cast<SharedStorage *>(ring_m + (size_t)C::kMeta * META_BYTES);
 
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // role index of this warp: the hardware warp GRWS_TC5_MMA_PHYS_WARP trades places with the
+    // MMA role's default slot, which decides which other roles share a scheduler with the MMA issuer
+    const int phys_warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int warp = phys_warp == GRWS_TC5_MMA_PHYS_WARP ? MMA_WARP : (phys_warp == MMA_WARP ? GRWS_TC5_MMA_PHYS_WARP : phys_warp);
     const int64_t W = prm.W;
 
     if (threadIdx.x == 0) {
@@ -732,15 +746,29 @@ int spmm_tc5_launch(const int64_t *window_offset, const int32_t *cols, const voi
     prm.partial = reinterpret_cast<float *>(static_cast<char *>(scratch) + STATUS_BYTES + DEBUG_BYTES + FIX_BYTES);
     prm.W = W; prm.N = N; prm.ldb = ldb; prm.ldc = ldc; prm.c_dtype = c_dtype;
     prm.is_bf16 = dtype == GRWS_BF16 ? 1 : 0;
-    const int G = grid_size() * (N == 128 ? Cfg<1>::kCtasPerSm : Cfg<2>::kCtasPerSm);
+    // Width 256: one pass with two slabs per stage (one CTA per SM), or two passes of 128 columns.
+    // Two passes read the tiles twice but gather from half as many bytes of the dense operand,
+    // which then stays in L2 next to the tile stream, and they run two CTAs per SM: measured 4 %
+    // faster at 86 MB of operand, 20 % at 119 MB.  Small operands keep the single pass (half the
+    // launches).  GRWS_TC5_SPLIT256 = 0 / 1 forces one way.
+    static const int split_env = [] { const char *e = getenv("GRWS_TC5_SPLIT256"); return e ? atoi(e) : -1; }();
+    const bool split = N == 256 && (split_env >= 0 ? split_env != 0 : K * 512 > SPLIT256_OPERAND_BYTES);
+    const int64_t pass_n = (N == 128 || split) ? 128 : 256;
+    const int G = grid_size() * (pass_n == 128 ? Cfg<1>::kCtasPerSm : Cfg<2>::kCtasPerSm);
     GRWS_CUDA_TRY(cudaMemsetAsync(scratch, 0, STATUS_BYTES, stream));
-    alignas(64) CUtensorMap b_map;
-    if (int st = encode_b_map(&b_map, B, prm.is_bf16, K, N, ldb)) return st;
-    GRWS_CUDA_TRY((N == 128 ? launch_kernel<1>(prm, b_map, G, stream) : launch_kernel<2>(prm, b_map, G, stream)));
-    GRWS_CUDA_TRY(cudaGetLastError());
-    if (G > 1) {
-        spmm_tc5_fixup_kernel<<<G, 1024, 0, stream>>>(prm, (int64_t)G);
+    const size_t c_elem = c_dtype == GRWS_F32 ? 4 : 2;
+    for (int64_t col0 = 0; col0 < N; col0 += pass_n) {
+        prm.B = static_cast<const char *>(B) + col0 * 2;
+        prm.C = static_cast<char *>(C) + col0 * c_elem;
+        prm.N = pass_n;
+        alignas(64) CUtensorMap b_map;
+        if (int st = encode_b_map(&b_map, prm.B, prm.is_bf16, K, pass_n, ldb)) return st;
+        GRWS_CUDA_TRY((pass_n == 128 ? launch_kernel<1>(prm, b_map, G, stream) : launch_kernel<2>(prm, b_map, G, stream)));
         GRWS_CUDA_TRY(cudaGetLastError());
+        if (G > 1) {
+            spmm_tc5_fixup_kernel<<<G, 1024, 0, stream>>>(prm, (int64_t)G);
+            GRWS_CUDA_TRY(cudaGetLastError());
+        }
     }
     return GRWS_OK;
 }

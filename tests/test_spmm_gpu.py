@@ -66,7 +66,9 @@ def test_tcgen05_matches_oracle_on_golden_graphs(oracle, path, dt, N):
 
 @pytest.mark.parametrize("dt,N,out", [("f16", 128, "f16"), ("bf16", 256, "f32"), ("f16", 256, "f32")])
 def test_tcgen05_power_law_graph(oracle, dt, N, out):
-    """Hub windows span several CTAs' tile ranges: exercises the partial tiles and the fix-up."""
+    """Hub windows span several CTAs' tile ranges: exercises the partial tiles and the fix-up.
+    With 20,000 rows the width-256 cases also take the two-pass route (128 columns per pass,
+    strided operand and output); the small golden graphs take the single two-slab pass."""
     from graph_rws_b200 import core
     from graph_rws_b200.data import synthetic
     g = synthetic.sym_normalized_csr(20000, *synthetic.chung_lu_edges(20000, 300000, 2.1, 23))
