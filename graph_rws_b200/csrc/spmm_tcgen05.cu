@@ -488,22 +488,25 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
         }
     } else if (warp >= PRODUCER_WARP0) {
         // ------------------------------------------------------------------ gather producers
-        // Two warps per pipeline stage: producer warps 2w and 2w+1 own gather slot w and fill every
-        // kStages-th stage, so the barrier polls and column-id reads of kStages stages overlap.
+        // Several warps per pipeline stage: producer warps k*w .. k*w+k-1 own gather slot w and fill
+        // every kStages-th stage, so the barrier polls and column-id reads of kStages stages overlap.
         // The rows are fetched by the TMA unit (tile::gather4): a lane issues the copy of four
-        // consecutive slots x 64 features; 16 lanes of each warp cover two of the stage's four
-        // K-steps (TMA instructions of different lanes issue one after the other, so the work of a
-        // stage is split between two warps).  The copies complete on the stage's barrier.
+        // consecutive slots x 64 features.  One warp issues a gather4 about every 220 cycles
+        // whatever the load (copies of different lanes go one after the other), while different
+        // warps issue in parallel, so a stage's 32 copies are spread over the warps of its slot.
+        // The copies complete on the stage's barrier.
         constexpr int WARPS_PER_SLOT = NUM_PRODUCER_WARPS / Cfg<NH>::kStages;
-        constexpr int OPS_PER_WARP = MMAS_PER_STAGE * 8 / WARPS_PER_SLOT;      // one copy per lane
+        constexpr int STAGE_OPS = MMAS_PER_STAGE * 8;                          // gather4 copies per stage and slab
         static_assert(WARPS_PER_SLOT >= 1 && WARPS_PER_SLOT * Cfg<NH>::kStages == NUM_PRODUCER_WARPS, "producer warps per slot");
-        static_assert(OPS_PER_WARP >= 1 && OPS_PER_WARP <= 32 && OPS_PER_WARP * WARPS_PER_SLOT == MMAS_PER_STAGE * 8, "copies per warp");
+        static_assert((STAGE_OPS + WARPS_PER_SLOT - 1) / WARPS_PER_SLOT <= 32, "one copy per lane");
         const uint64_t keep = policy_keep();
         const int pwarp = warp - PRODUCER_WARP0;
         const int member = pwarp % WARPS_PER_SLOT;
-        const bool issuer = lane < OPS_PER_WARP;
-        const int op = member * OPS_PER_WARP + lane;          // (K-step, slot group, feature half) of this lane's copy
-        const int m = op >> 3, grp = (op >> 1) & 3, half = op & 1;
+        // the copies of a stage are dealt round-robin to the warps of its slot, one per lane
+        const int op = member + lane * WARPS_PER_SLOT;        // (K-step, slot group, feature half) of this lane's copy
+        const bool issuer = op < STAGE_OPS;
+        const int opc = issuer ? op : 0;                      // idle lanes compute in-range addresses, they copy nothing
+        const int m = opc >> 3, grp = (opc >> 1) & 3, half = opc & 1;
         // slots 4*grp .. 4*grp+3 of K-step m: slot half grp / 2, lines (4*grp) % 8 .. +3 of the atom
         const uint32_t lane_off = (uint32_t)(m * NH * A_MMA_BYTES + (grp >> 1) * A_SBO + half * A_LBO + ((4 * grp) & 7) * 128);
         long long w_full_m = 0, w_empty_g = 0;
