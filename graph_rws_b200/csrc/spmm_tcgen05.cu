@@ -295,7 +295,10 @@ template <int NH> struct Cfg {
     static constexpr int kStages = GRWS_TC5_STAGES;
     // tile / column-id slots: the TMA warp runs kMeta - kStages stages ahead of the data it has
     // already landed, which has to cover the HBM latency of the tile stream
-    static constexpr int kMeta = kStages + ((NH == 1) ? 12 : 16) * 8 / STAGE_TILES;
+#ifndef GRWS_TC5_META_AHEAD
+#define GRWS_TC5_META_AHEAD 12
+#endif
+    static constexpr int kMeta = kStages + ((NH == 1) ? GRWS_TC5_META_AHEAD : 16) * 8 / STAGE_TILES;
     static constexpr int kStageBytes = MMAS_PER_STAGE * NH * A_MMA_BYTES;
     static constexpr int kAccCols = 16 * NH;
     static constexpr int kTmemCols = (NACC * kAccCols) < 32 ? 32 : NACC * kAccCols;   // 64 or 128: powers of two
@@ -788,7 +791,7 @@ int spmm_tc5_launch(const int64_t *window_offset, const int32_t *cols, const voi
 // status word, the per-CTA fix-up records and the fp32 partial tiles of windows that were split
 // between CTAs) lives in the fixed array below instead of a caller-provided buffer.
 //
-//   * The array is STATIC_SCRATCH_BYTES (about 11 MB) and every GPU that loads the library keeps
+//   * The array is STATIC_SCRATCH_BYTES (about 21 MB) and every GPU that loads the library keeps
 //     it until the process exits.  It is sized for dense widths up to 256 on a device with up to
 //     160 SMs; anything that would need more is rejected with GRWS_ERR_SCRATCH.
 //   * In host code the array's name is only a host-side handle, not a device address.  The device
