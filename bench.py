@@ -454,6 +454,19 @@ def run_secondary(args):
             sampler.sample_layers(graph, seeds_for_step())
         barrier()
         extra["sampling_only_seeds_per_s"] = world * per_gpu * n_s / (time.perf_counter() - t0)
+        # the same step with batch i+1 sampled on a side stream by a producer thread while batch i trains
+        from graph_rws_b200.helper import train_epoch_node_sampling
+        n_p = 40
+        train_dev = train.to(device)
+        for pipe in (False, True):
+            lo = rank * per_gpu * n_p
+            idx = train_dev[lo:lo + per_gpu * n_p]
+            train_epoch_node_sampling(model, graph, x, y, idx[:per_gpu * 4], opt, sampler, batch_size=per_gpu, pipeline=pipe)
+            barrier()
+            t0 = time.perf_counter()
+            train_epoch_node_sampling(model, graph, x, y, idx, opt, sampler, batch_size=per_gpu, pipeline=pipe)
+            barrier()
+            extra["epoch_seeds_per_s_pipelined" if pipe else "epoch_seeds_per_s_serial"] = world * idx.numel() / (time.perf_counter() - t0)
 
     for _ in range(max(args.warmup, 3)):
         step()

@@ -147,12 +147,18 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     }
 }
 // wait that adds its duration to `acc` in the profiling build of the kernel
+__device__ unsigned long long g_prof_tries[8];     // profiling build: failed try_waits per role
 template <bool PROF>
-__device__ __forceinline__ bool mbar_wait_t(uint32_t bar, uint32_t parity, volatile int *abort_flag, long long &acc) {
+__device__ __forceinline__ bool mbar_wait_t(uint32_t bar, uint32_t parity, volatile int *abort_flag, long long &acc, int role = 0) {
     if constexpr (PROF) {
         const long long t0 = clock64();
-        const bool ok = mbar_wait(bar, parity, abort_flag);
+        unsigned long long tries = 0;
+        bool ok = false;
+        for (; tries < 100000000ull; ++tries)
+            if (mbar_try_wait(bar, parity)) { ok = true; break; }
         acc += clock64() - t0;
+        if (tries) atomicAdd(&g_prof_tries[role], tries);
+        (void)abort_flag;
         return ok;
     } else {
         return mbar_wait(bar, parity, abort_flag);
@@ -376,7 +382,7 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
                     if (it % NUM_META_WARPS != meta_id) continue;      // another meta warp's stage
                     const uint32_t slot = it % C::kMeta, ph = (it / C::kMeta) & 1u;
                     const int ntiles = (int)min((int64_t)STAGE_TILES, wk.seg_e - t0);
-                    if (lane == 0) ok = mbar_wait_t<PROF>(smem_u32(&ss->empty_m[slot]), ph ^ 1u, abort_flag, w_empty_m);
+                    if (lane == 0) ok = mbar_wait_t<PROF>(smem_u32(&ss->empty_m[slot]), ph ^ 1u, abort_flag, w_empty_m, 5);
                     ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
                     if (ok && (ntiles & 1)) {
                         // an odd tile count leaves the second tile of the last K-step without data:
@@ -440,7 +446,7 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
                     ++ai;
                     // one polling lane per warp: threads spinning on a barrier slow every other
                     // barrier operation of the SM down
-                    if (lane == 0) ok = mbar_wait_t<PROF>(smem_u32(&ss->acc_full[buf]), aph, abort_flag, w_af);
+                    if (lane == 0) ok = mbar_wait_t<PROF>(smem_u32(&ss->acc_full[buf]), aph, abort_flag, w_af, 4);
                     ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
                     if (!ok) { if (lane == 0) raise(prm, ss, ST_TIMEOUT_ACC); break; }
                     tc_fence_after();
@@ -521,7 +527,7 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
             const uint32_t ms = it % C::kMeta, mph = (it / C::kMeta) & 1u;
             // column ids and the command have landed
             bool ok = true;
-            if (lane == 0) ok = mbar_wait_t<PROF>(smem_u32(&ss->full_m[ms]), mph, abort_flag, w_full_m);
+            if (lane == 0) ok = mbar_wait_t<PROF>(smem_u32(&ss->full_m[ms]), mph, abort_flag, w_full_m, 3);
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
             if (!ok) { if (lane == 0) raise(prm, ss, ST_TIMEOUT_META); break; }
             if (lane == 0) prof_mark<PROF>(prm.dbg, it, 1);
@@ -536,7 +542,7 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
             int4 c = *reinterpret_cast<const int4 *>(meta + META_TILE_BYTES + slot0 * 4);
             if (slot0 >= nvalid) c = make_int4(-1, -1, -1, -1);
             // the gather slot has been released by the MMA warp (it finished stage it - kStages)
-            if (lane == 0) ok = mbar_wait_t<PROF>(empty_bar, gph ^ 1u, abort_flag, w_empty_g);
+            if (lane == 0) ok = mbar_wait_t<PROF>(empty_bar, gph ^ 1u, abort_flag, w_empty_g, 2);
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
             if (!ok) { if (lane == 0) raise(prm, ss, ST_TIMEOUT_EMPTY); break; }
             if (lane == 0) prof_mark<PROF>(prm.dbg, it, 2);
@@ -574,7 +580,7 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
             for (;; ++it) {
                 // The producers arrive on full_g only after they have seen full_m of the same stage,
                 // so this one wait also covers the tile values and the command word.
-                if (!mbar_wait_t<PROF>(smem_u32(&ss->full_g[gs]), gph, abort_flag, w_fg)) { raise(prm, ss, ST_TIMEOUT_FULL); break; }
+                if (!mbar_wait_t<PROF>(smem_u32(&ss->full_g[gs]), gph, abort_flag, w_fg, 1)) { raise(prm, ss, ST_TIMEOUT_FULL); break; }
                 prof_mark<PROF>(prm.dbg, it, 5);
                 const long long tc0 = prof_clock<PROF>();
                 const uint32_t cmd = *reinterpret_cast<const volatile uint32_t *>(ring_m + ms * META_BYTES + META_TILE_BYTES + META_COL_BYTES);
@@ -775,6 +781,11 @@ int spmm_tc5_launch(const int64_t *window_offset, const int32_t *cols, const voi
             spmm_tc5_fixup_kernel<<<G, 1024, 0, stream>>>(prm, (int64_t)G);
             GRWS_CUDA_TRY(cudaGetLastError());
         }
+    }
+    if (prm.dbg) {      // profiling build: failed try_waits per role since the last call, behind the timeline
+        GRWS_CUDA_TRY(cudaMemcpyFromSymbolAsync(prm.dbg + 12288 + 64 * 8, g_prof_tries, sizeof(g_prof_tries), 0, cudaMemcpyDeviceToDevice, stream));
+        static const unsigned long long zeros[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        GRWS_CUDA_TRY(cudaMemcpyToSymbolAsync(g_prof_tries, zeros, sizeof(zeros), 0, cudaMemcpyHostToDevice, stream));
     }
     return GRWS_OK;
 }

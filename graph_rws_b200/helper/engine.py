@@ -7,6 +7,9 @@ clipping at 1.0, optimizer step.  With per-node sampled blocks the seed -> logit
 helper/engine.py:175-183 (a searchsorted over ``active_windows``) becomes the identity on the first
 ``len(seeds)`` rows.  Data-parallel ranks all-reduce the gradients (NCCL) before the step.
 """
+import queue
+import threading
+
 import torch
 import torch.distributed as dist
 import torch.nn.functional as F
@@ -73,3 +76,94 @@ def train_step_sampled(model, sampler, graph, features, labels, seeds, optimizer
     torch.nn.utils.clip_grad_norm_(model.parameters(), max_norm=1.0)
     optimizer.step()
     return loss.detach()
+
+
+def _record_stream(obj, stream):
+    """Tell the caching allocator that ``stream`` uses the tensors of ``obj`` (a tensor, a block or a
+    list of them), which were allocated on another stream."""
+    if torch.is_tensor(obj):
+        if obj.is_cuda:
+            obj.record_stream(stream)
+    elif isinstance(obj, (list, tuple)):
+        for o in obj:
+            _record_stream(o, stream)
+    elif hasattr(obj, '__dict__'):
+        for v in vars(obj).values():
+            if torch.is_tensor(v) or isinstance(v, (list, tuple)):
+                _record_stream(v, stream)
+
+
+def train_epoch_node_sampling(model, graph, features, labels, train_idx, optimizer, sampler,
+                              batch_size: int = 1024, pipeline: bool = True, fetch_rows=None, max_batches=None):
+    """One epoch of mini-batch training over ``train_idx`` (helper/engine.py:86-256).
+
+    With ``pipeline`` a producer thread samples the blocks of batch i+1 and gathers its input rows
+    on a side stream while the main thread trains on batch i (the reference's producer / consumer
+    pair with a queue of one, helper/engine.py:118-153); the hand-over is a CUDA event, so neither
+    thread synchronises the device.  Returns (mean loss tensor, number of seeds trained on)."""
+    device = labels.device
+    n = train_idx.numel()
+    starts = list(range(0, n, batch_size))
+    if max_batches is not None:
+        starts = starts[:max_batches]
+    main_stream = torch.cuda.current_stream(device)
+    total = torch.zeros((), device=device)
+    model.train()
+
+    def make_batch(step, lo):
+        seeds = train_idx[lo:lo + batch_size].to(device=device, dtype=torch.int32, non_blocking=True)
+        sampler.step = step
+        blocks = sampler.sample_layers(graph, seeds)
+        ids = blocks[0].input_nodes.clamp(min=0)
+        x = fetch_rows(ids) if fetch_rows is not None else features[ids.long()]
+        return seeds, blocks, x
+
+    def train_on(seeds, blocks, x):
+        optimizer.zero_grad(set_to_none=True)
+        logits = model(blocks, x)[:seeds.numel()]
+        loss = F.cross_entropy(logits.float(), labels[seeds.long()])
+        loss.backward()
+        _allreduce_grads(model)
+        torch.nn.utils.clip_grad_norm_(model.parameters(), max_norm=1.0)
+        optimizer.step()
+        return loss.detach()
+
+    if not pipeline:
+        for step, lo in enumerate(starts):
+            total += train_on(*make_batch(step, lo))
+        return total / max(len(starts), 1), min(n, len(starts) * batch_size)
+
+    side = torch.cuda.Stream(device)
+    side.wait_stream(main_stream)
+    q = queue.Queue(maxsize=1)
+    failure = []
+
+    def producer():
+        try:
+            torch.cuda.set_device(device)
+            with torch.cuda.stream(side):
+                for step, lo in enumerate(starts):
+                    item = make_batch(step, lo)
+                    ev = torch.cuda.Event()
+                    ev.record(side)
+                    q.put((item, ev))
+        except BaseException as exc:      # hand the failure to the consumer instead of dying silently
+            failure.append(exc)
+        finally:
+            q.put(None)
+
+    worker = threading.Thread(target=producer, daemon=True)
+    worker.start()
+    while True:
+        got = q.get()
+        if got is None:
+            break
+        (seeds, blocks, x), ev = got
+        main_stream.wait_event(ev)
+        _record_stream([seeds, blocks, x], main_stream)
+        total += train_on(seeds, blocks, x)
+    worker.join()
+    if failure:
+        raise failure[0]
+    side.wait_stream(main_stream)
+    return total / max(len(starts), 1), min(n, len(starts) * batch_size)
