@@ -36,7 +36,7 @@ namespace tc5 {
 #define GRWS_TC5_STAGE_TILES 8
 #endif
 #ifndef GRWS_TC5_STAGES
-#define GRWS_TC5_STAGES 4
+#define GRWS_TC5_STAGES 5
 #endif
 constexpr int STAGE_TILES = GRWS_TC5_STAGE_TILES;    // tiles per pipeline stage (two per MMA K-step)
 constexpr int STAGE_SLOTS = STAGE_TILES * TILE_COLS; // gathered rows per stage
@@ -62,7 +62,10 @@ constexpr uint32_t CMD_COUNT = 31u, CMD_FIRST = 1u << 8, CMD_LAST = 1u << 9, CMD
 static_assert(STAGE_TILES <= (int)CMD_COUNT && STAGE_TILES % 2 == 0, "tile count field of the command word");
 constexpr int NACC = 4;                              // accumulator buffers in tensor memory
 #ifndef GRWS_TC5_PRODUCER_WARPS
-#define GRWS_TC5_PRODUCER_WARPS 8
+#define GRWS_TC5_PRODUCER_WARPS 5
+#endif
+#ifndef GRWS_TC5_NO_ELECT
+#define GRWS_TC5_ELECT 1     // TMA copies and MMAs are issued by one elected lane with warp-uniform operands
 #endif
 constexpr int NUM_PRODUCER_WARPS = GRWS_TC5_PRODUCER_WARPS;   // a multiple of the stage count
 constexpr int NUM_EPILOGUE = 128;
@@ -70,7 +73,7 @@ constexpr int EPILOGUE_WARP0 = 0;                        // four warps; warp % 4
 constexpr int MMA_WARP = EPILOGUE_WARP0 + 4;
 constexpr int TMA_WARP = MMA_WARP + 1;
 #ifndef GRWS_TC5_META_WARPS
-#define GRWS_TC5_META_WARPS 2
+#define GRWS_TC5_META_WARPS 1
 #endif
 constexpr int NUM_META_WARPS = GRWS_TC5_META_WARPS;     // they take the stages round-robin
 constexpr int PRODUCER_WARP0 = TMA_WARP + NUM_META_WARPS;
@@ -154,8 +157,12 @@ __device__ __forceinline__ bool mbar_wait_t(uint32_t bar, uint32_t parity, volat
         const long long t0 = clock64();
         unsigned long long tries = 0;
         bool ok = false;
-        for (; tries < 100000000ull; ++tries)
+        for (; tries < 100000000ull; ++tries) {
             if (mbar_try_wait(bar, parity)) { ok = true; break; }
+#ifdef GRWS_TC5_BACKOFF
+            __nanosleep(GRWS_TC5_BACKOFF);
+#endif
+        }
         acc += clock64() - t0;
         if (tries) atomicAdd(&g_prof_tries[role], tries);
         (void)abort_flag;
@@ -191,6 +198,12 @@ __device__ __forceinline__ void tma_gather4(uint32_t dst, const CUtensorMap *map
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes.L2::cache_hint"
                  " [%0], [%1, {%3, %4, %5, %6, %7}], [%2], %8;"
                  ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(r0), "r"(r1), "r"(r2), "r"(r3), "l"(pol) : "memory");
+}
+// true in exactly one lane of a converged warp
+__device__ __forceinline__ bool elect_one() {
+    uint32_t e;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(e));
+    return e != 0;
 }
 __device__ __forceinline__ uint64_t policy_keep() {
     uint64_t p;
@@ -302,7 +315,7 @@ template <int NH> struct Cfg {
     // tile / column-id slots: the TMA warp runs kMeta - kStages stages ahead of the data it has
     // already landed, which has to cover the HBM latency of the tile stream
 #ifndef GRWS_TC5_META_AHEAD
-#define GRWS_TC5_META_AHEAD 12
+#define GRWS_TC5_META_AHEAD 6
 #endif
     static constexpr int kMeta = kStages + ((NH == 1) ? GRWS_TC5_META_AHEAD : 16) * 8 / STAGE_TILES;
     static constexpr int kStageBytes = MMAS_PER_STAGE * NH * A_MMA_BYTES;
@@ -329,7 +342,9 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
 
     // role index of this warp: the hardware warp GRWS_TC5_MMA_PHYS_WARP trades places with the
     // MMA role's default slot, which decides which other roles share a scheduler with the MMA issuer
-    const int phys_warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // the warp index is taken from lane 0 so that the compiler knows it is the same in all lanes:
+    // everything derived from it (role, barrier and ring addresses) can live in uniform registers
+    const int phys_warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
     const int warp = phys_warp == GRWS_TC5_MMA_PHYS_WARP ? MMA_WARP : (phys_warp == MMA_WARP ? GRWS_TC5_MMA_PHYS_WARP : phys_warp);
     const int64_t W = prm.W;
 
@@ -392,7 +407,12 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
                         fence_async_smem();
                         __syncwarp();
                     }
+#ifdef GRWS_TC5_ELECT
+                    __syncwarp();
+                    if (elect_one()) {
+#else
                     if (lane == 0) {
+#endif
                         if (ok) {
                             const uint32_t bar = smem_u32(&ss->full_m[slot]);
                             uint8_t *dst = ring_m + (size_t)slot * META_BYTES;
@@ -557,17 +577,46 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
                 if (prm.skip & 2) mbar_arrive(full_bar);          // experiment: no gathers, nothing to wait for
                 else mbar_expect_tx(full_bar, (uint32_t)(nmma * 16 * SLAB * 2 * NH));
             }
+#ifdef GRWS_TC5_ELECT
+            // one elected lane issues all of this warp's copies: its operands are uniform but the row ids
+            __syncwarp();
+            if (elect_one() && !(prm.skip & 2)) {
+                constexpr int MAX_OPS = (STAGE_OPS + WARPS_PER_SLOT - 1) / WARPS_PER_SLOT;
+                const uint32_t dst_slot = smem_u32(ring_g + (size_t)gs * C::kStageBytes);
+#pragma unroll
+                for (int j = 0; j < MAX_OPS; ++j) {
+                    const int o = member + j * WARPS_PER_SLOT;
+                    const int om = o >> 3, og = (o >> 1) & 3, oh = o & 1;
+                    if (o < STAGE_OPS && om < nmma) {
+                        const int s0 = 16 * om + 4 * og;
+                        int4 r = *reinterpret_cast<const int4 *>(meta + META_TILE_BYTES + s0 * 4);
+                        if (s0 >= nvalid) r = make_int4(-1, -1, -1, -1);
+                        const uint32_t off = (uint32_t)(om * NH * A_MMA_BYTES + (og >> 1) * A_SBO + oh * A_LBO + ((4 * og) & 7) * 128);
+#pragma unroll
+                        for (int h = 0; h < NH; ++h)
+                            tma_gather4(dst_slot + off + (uint32_t)(h * A_MMA_BYTES), &b_map, full_bar, h * SLAB + oh * 64, r.x, r.y, r.z, r.w, keep);
+                    }
+                }
+            }
+            __syncwarp();
+            (void)issuer; (void)c; (void)dst; (void)half; (void)m;
+#else
             if (issuer && m < nmma && !(prm.skip & 2)) {
 #pragma unroll
                 for (int h = 0; h < NH; ++h)
                     tma_gather4(dst + (uint32_t)(h * A_MMA_BYTES), &b_map, full_bar, h * SLAB + half * 64, c.x, c.y, c.z, c.w, keep);
             }
+#endif
             if (lane == 0) prof_mark<PROF>(prm.dbg, it, 3);
         }
         if (PROF && prm.dbg && threadIdx.x == PRODUCER_WARP0 * 32) { prm.dbg[blockIdx.x * 16 + 2] = w_full_m; prm.dbg[blockIdx.x * 16 + 3] = w_empty_g; }
     } else if (warp == MMA_WARP) {
         // ------------------------------------------------------------------ MMA issuer (one thread)
+#ifdef GRWS_TC5_ELECT
+        if (elect_one()) {
+#else
         if (lane == 0) {
+#endif
             const uint32_t idesc = (1u << 4) | ((uint32_t)prm.is_bf16 << 7) | ((uint32_t)prm.is_bf16 << 10) |
                                    (1u << 15) | ((16u >> 3) << 17) | ((128u >> 4) << 24);
             // descriptors of stage 0 / meta slot 0; other stages add their byte offset >> 4 to the low word
