@@ -145,6 +145,10 @@ def run_ours(args):
     bytes_fwd = algorithmic_bytes(graph, csr.num_nodes, width, esize, torch)
     bytes_bwd = algorithmic_bytes(graph_t, csr.num_nodes, width, esize, torch)
     bytes_step = bytes_fwd + bytes_bwd
+    # kernels of this library per step: the tcgen05 path is one launch per product (two for width
+    # 256 above 8 MB of operand), the warp-MMA path a main kernel plus its fix-up kernel
+    tc5 = args.algo != "warp" and dt in ("f16", "bf16") and width in (128, 256)
+    launches_per_step = 2 * ((2 if (width == 256 and csr.num_nodes * 512 > (8 << 20)) else 1) if tc5 else 2)
 
     def step():
         c = core.spmm_raw(graph.window_offset, graph.original_col_indices, graph.values_condensed, H)
@@ -259,7 +263,7 @@ def run_ours(args):
                     "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": int(H_pin.numel() + G_pin.numel()) * esize,
                     "d2h_bytes_per_step": int(C_pin.numel() + D_pin.numel()) * esize},
-            "gpu_launches": 4 * args.steps,
+            "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks,
         }
         if cpu_base is not None:

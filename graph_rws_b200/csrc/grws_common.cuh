@@ -53,8 +53,8 @@ inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 // most `long_window` tiles is moved back to that window's first tile, so only long windows are
 // ever split between two work items.  Item k covers tiles [cut(k), cut(k+1)) and owns every
 // window whose last tile lies in that range (plus, for item 0, leading empty windows).
-// A split window's pieces are written as fp32 partial tiles to scratch and summed in a fixed
-// order by the fix-up kernel, so results do not depend on scheduling.
+// A split window's pieces are written as fp32 partial tiles to scratch and summed in item order
+// (by a fix-up kernel, or by the item that finishes last), so results do not depend on scheduling.
 // ---------------------------------------------------------------------------------------------
 
 // number of windows w in [0, W) with window_offset[w + 1] <= x, found by one warp with a 32-ary

@@ -16,12 +16,12 @@
 //   * accumulators live in tensor memory (16 fp32 columns per slab), four deep, so the epilogue
 //     of one window overlaps the MMAs of the next.
 //
-// One persistent CTA per SM owns a contiguous range of the global tile array (equal tile counts,
-// so power-law window lengths do not matter); a window cut by a range boundary is finished by the
-// fix-up kernel from fp32 partial tiles in scratch, in a fixed order.
+// Persistent CTAs each own a contiguous range of the global tile array (equal tile counts, so
+// power-law window lengths do not matter); the pieces of a window cut by a range boundary go to
+// scratch as fp32 partial tiles and the CTA that finishes its piece last sums them in CTA order.
 //
-// Warp roles: 0-3 epilogue (TMEM -> registers -> global), 4 MMA issuer, 5-6 TMA producers for tile
-// values and column ids (alternating stages), 7.. gather producers (two per pipeline stage).  Every mbarrier wait is bounded: on time-out the
+// Warp roles: 0-3 epilogue (TMEM -> registers -> global), 4 MMA issuer, 5 TMA producer for tile
+// values and column ids, 6.. gather producers (one per ring slot).  Every mbarrier wait is bounded: on time-out the
 // kernel raises the status word at the start of scratch and all roles drain and return.
 #include <cuda.h>      // CUtensorMap and the cuTensorMapEncodeTiled prototype (resolved at run time)
 #include <stdlib.h>
@@ -96,7 +96,7 @@ struct Params {
     void *C;
     float *partial;
     int *status;
-    int64_t *fix;     // [grid][4]: range start, window whose first piece this CTA holds (-1: none), its end, unused
+    int *split_count; // [grid]: pieces of the split window that starts in CTA k which are finished (zeroed before the launch)
     int64_t W, N, ldb, ldc;
     int c_dtype;
     int is_bf16;
@@ -302,6 +302,7 @@ struct SharedStorage {
     uint64_t full_g[16], empty_g[16], full_m[64], empty_m[64], acc_full[NACC], acc_empty[NACC];
     uint32_t tmem_base;
     int abort_flag;
+    int last_piece;       // epilogue: this CTA finished the last piece of a split window
 };
 
 template <int NH> struct Cfg {
@@ -455,10 +456,8 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
             uint32_t ai = 0;
             bool ok = true;
             long long w_af = 0;
-            int64_t tail_w = -1, tail_b = 0;
             while (ok && wk.next_segment(lane)) {
                 const int64_t w = wk.window();
-                if (wk.tail()) { tail_w = w; tail_b = wk.b; }
                 const bool nonempty = wk.seg_e > wk.seg_s;
                 uint32_t v[NH][16];
                 if (nonempty) {
@@ -508,10 +507,46 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
                         for (int r = 0; r < 16; ++r) slot[(int64_t)r * prm.N + f] = __uint_as_float(v[h][r]);
                     }
                 }
-            }
-            if (threadIdx.x == EPILOGUE_WARP0 * 32) {       // what the fix-up kernel needs to know
-                int64_t *fx = prm.fix + 4 * (int64_t)blockIdx.x;
-                fx[0] = s; fx[1] = tail_w; fx[2] = tail_b;
+                if (partial && !(prm.skip & 4)) {
+                    // A window cut between CTAs: every holder of a piece counts itself on the counter of
+                    // the CTA that holds the window's first tile, and the one that arrives last sums the
+                    // pieces in CTA order (the same order whoever is last) and writes the rows.  Cuts
+                    // inside a split window are never moved, so its pieces are exactly the CTAs
+                    // a / chunk .. (b - 1) / chunk.
+                    __threadfence();
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    const int64_t k0 = wk.a / chunk, k_last = (wk.b - 1) / chunk;
+                    if (threadIdx.x == 0) {
+                        const int old = atomicAdd(prm.split_count + k0, 1);
+                        ss->last_piece = (old == (int)(k_last - k0)) ? 1 : 0;
+                    }
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    if (*reinterpret_cast<volatile int *>(&ss->last_piece)) {
+                        __threadfence();
+                        const int64_t elems = TILE_ROWS * prm.N;
+#pragma unroll
+                        for (int h = 0; h < NH; ++h) {
+                            const int64_t f = h * SLAB + 32 * q + lane;
+                            float acc[16];
+                            const float *p0 = prm.partial + (2 * k0 + 1) * elems + f;
+#pragma unroll
+                            for (int r = 0; r < 16; ++r) acc[r] = __ldcg(p0 + (int64_t)r * prm.N);
+                            for (int64_t kq = k0 + 1; kq <= k_last; ++kq) {
+                                const float *pq = prm.partial + (2 * kq) * elems + f;
+#pragma unroll
+                                for (int r = 0; r < 16; ++r) acc[r] += __ldcg(pq + (int64_t)r * prm.N);
+                            }
+                            const int64_t base = (w * TILE_ROWS) * prm.ldc + f;
+#pragma unroll
+                            for (int r = 0; r < 16; ++r) {
+                                const int64_t o = base + r * prm.ldc;
+                                if (prm.c_dtype == GRWS_F32) static_cast<float *>(prm.C)[o] = acc[r];
+                                else if (prm.c_dtype == GRWS_F16) static_cast<__half *>(prm.C)[o] = __float2half_rn(acc[r]);
+                                else static_cast<__nv_bfloat16 *>(prm.C)[o] = __float2bfloat16_rn(acc[r]);
+                            }
+                        }
+                    }
+                }
             }
             if (PROF && prm.dbg && threadIdx.x == EPILOGUE_WARP0 * 32) prm.dbg[blockIdx.x * 16 + 7] = w_af;
         }
@@ -689,33 +724,6 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
     }
 }
 
-// Sums the partial tiles of the windows that were split between CTAs, in CTA order.  CTA k of the
-// main kernel recorded whether it holds the first piece of a split window (and where that window
-// ends) and every CTA recorded where its tile range starts; the following CTAs whose range starts
-// inside the window hold its other pieces.
-__global__ void __launch_bounds__(1024)
-spmm_tc5_fixup_kernel(const Params prm, int64_t G) {
-    const int64_t k = blockIdx.x;
-    const int64_t *fx = prm.fix + 4 * k;
-    const int64_t w = fx[1];
-    if (w < 0) return;
-    const int64_t b = fx[2];
-    int64_t k_last = k;
-    while (k_last + 1 < G && prm.fix[4 * (k_last + 1)] < b) ++k_last;
-    const int64_t N = prm.N, elems = TILE_ROWS * N;
-    // one or two elements per thread: the loads of a thread are a dependent chain, so the kernel's
-    // duration is that chain's length, not the (tiny) amount of data
-    for (int64_t i = threadIdx.x; i < elems; i += blockDim.x) {
-        float v = prm.partial[(2 * k + 1) * elems + i];                                   // first piece
-        for (int64_t q = k + 1; q <= k_last; ++q) v += prm.partial[(2 * q) * elems + i];   // later pieces
-        const int64_t r = i / N, f = i % N;
-        const int64_t o = (w * TILE_ROWS + r) * prm.ldc + f;
-        if (prm.c_dtype == GRWS_F32) static_cast<float *>(prm.C)[o] = v;
-        else if (prm.c_dtype == GRWS_F16) static_cast<__half *>(prm.C)[o] = __float2half_rn(v);
-        else static_cast<__nv_bfloat16 *>(prm.C)[o] = __float2bfloat16_rn(v);
-    }
-}
-
 static int grid_size() {
     static const int sms = [] {
         int dev = 0, n = 0;
@@ -728,7 +736,7 @@ static int grid_size() {
 
 constexpr size_t STATUS_BYTES = 256;
 constexpr size_t DEBUG_BYTES = 1024 * 16 * sizeof(long long);
-constexpr size_t FIX_BYTES = 1024 * 4 * sizeof(int64_t);      // per-CTA fix-up records   // per-CTA wait counters (GRWS_TC5_PROFILE=1)
+constexpr size_t FIX_BYTES = 1024 * 4 * sizeof(int64_t);      // per-CTA counters of finished pieces of split windows
 
 static bool profile_waits() {
     static const int v = [] { const char *e = getenv("GRWS_TC5_PROFILE"); return e ? atoi(e) : 0; }();
@@ -802,8 +810,9 @@ int spmm_tc5_launch(const int64_t *window_offset, const int32_t *cols, const voi
     prm.status = static_cast<int *>(scratch);
     { static const int sk = [] { const char *e = getenv("GRWS_TC5_SKIP"); return e ? atoi(e) : 0; }(); prm.skip = sk; }
     { static const int lw = [] { const char *e = getenv("GRWS_TC5_LW_SHIFT"); return e ? atoi(e) : 4; }(); prm.lw_shift = lw; }
-    prm.dbg = profile_waits() ? reinterpret_cast<long long *>(static_cast<char *>(scratch) + STATUS_BYTES) : nullptr;
-    prm.fix = reinterpret_cast<int64_t *>(static_cast<char *>(scratch) + STATUS_BYTES + DEBUG_BYTES);
+    // layout: status word | split-window counters | profiling counters | partial tiles; the first two are zeroed together
+    prm.dbg = profile_waits() ? reinterpret_cast<long long *>(static_cast<char *>(scratch) + STATUS_BYTES + FIX_BYTES) : nullptr;
+    prm.split_count = reinterpret_cast<int *>(static_cast<char *>(scratch) + STATUS_BYTES);
     prm.partial = reinterpret_cast<float *>(static_cast<char *>(scratch) + STATUS_BYTES + DEBUG_BYTES + FIX_BYTES);
     prm.W = W; prm.N = N; prm.ldb = ldb; prm.ldc = ldc; prm.c_dtype = c_dtype;
     prm.is_bf16 = dtype == GRWS_BF16 ? 1 : 0;
@@ -816,7 +825,6 @@ int spmm_tc5_launch(const int64_t *window_offset, const int32_t *cols, const voi
     const bool split = N == 256 && (split_env >= 0 ? split_env != 0 : K * 512 > SPLIT256_OPERAND_BYTES);
     const int64_t pass_n = (N == 128 || split) ? 128 : 256;
     const int G = grid_size() * (pass_n == 128 ? Cfg<1>::kCtasPerSm : Cfg<2>::kCtasPerSm);
-    GRWS_CUDA_TRY(cudaMemsetAsync(scratch, 0, STATUS_BYTES, stream));
     const size_t c_elem = c_dtype == GRWS_F32 ? 4 : 2;
     for (int64_t col0 = 0; col0 < N; col0 += pass_n) {
         prm.B = static_cast<const char *>(B) + col0 * 2;
@@ -824,12 +832,11 @@ int spmm_tc5_launch(const int64_t *window_offset, const int32_t *cols, const voi
         prm.N = pass_n;
         alignas(64) CUtensorMap b_map;
         if (int st = encode_b_map(&b_map, prm.B, prm.is_bf16, K, pass_n, ldb)) return st;
+        // the status word is cleared once per call, the split-window counters before every pass
+        if (col0 == 0) GRWS_CUDA_TRY(cudaMemsetAsync(scratch, 0, STATUS_BYTES + sizeof(int) * (size_t)G, stream));
+        else GRWS_CUDA_TRY(cudaMemsetAsync(prm.split_count, 0, sizeof(int) * (size_t)G, stream));
         GRWS_CUDA_TRY((pass_n == 128 ? launch_kernel<1>(prm, b_map, G, stream) : launch_kernel<2>(prm, b_map, G, stream)));
         GRWS_CUDA_TRY(cudaGetLastError());
-        if (G > 1) {
-            spmm_tc5_fixup_kernel<<<G, 1024, 0, stream>>>(prm, (int64_t)G);
-            GRWS_CUDA_TRY(cudaGetLastError());
-        }
     }
     if (prm.dbg) {      // profiling build: failed try_waits per role since the last call, behind the timeline
         GRWS_CUDA_TRY(cudaMemcpyFromSymbolAsync(prm.dbg + 12288 + 64 * 8, g_prof_tries, sizeof(g_prof_tries), 0, cudaMemcpyDeviceToDevice, stream));
@@ -848,7 +855,7 @@ int spmm_tc5_launch(const int64_t *window_offset, const int32_t *cols, const voi
 // another framework's stream-ordered or pooled allocator and is handed only its input and output
 // buffers, a real-time inference loop whose memory was frozen at start-up, a caller that is in
 // the middle of capturing work it does not own.  For them the scratch of the tcgen05 kernel (its
-// status word, the per-CTA fix-up records and the fp32 partial tiles of windows that were split
+// status word, the per-CTA split-window counters and the fp32 partial tiles of windows that were split
 // between CTAs) lives in the fixed array below instead of a caller-provided buffer.
 //
 //   * The array is STATIC_SCRATCH_BYTES (about 21 MB) and every GPU that loads the library keeps

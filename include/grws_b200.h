@@ -85,7 +85,7 @@ int grws_spmm_fwd(const int64_t *window_offset, const int32_t *cols, const void 
  * the reference.  It exists for callers that cannot provide device scratch: code that runs
  * inside another framework's memory pool and only receives its input and output buffers, a
  * serving loop whose device memory was fixed at start-up, a host that must not call cudaMalloc
- * at this point.  The kernel's scratch (status word, per-CTA fix-up records, fp32 partial tiles
+ * at this point.  The kernel's scratch (status word, per-CTA split-window counters, fp32 partial tiles
  * of windows split between CTAs) lives in a fixed array inside the library instead:
  *   - GRWS_SPMM_STATIC_SCRATCH_BYTES (about 21 MB) per GPU that loads the library, held until
  *     the process exits; sized for N <= 256 on devices with up to 160 SMs -- a call that would
