@@ -287,7 +287,27 @@ struct Walker {
         if (w >= W) return false;
         a = os.get(w, lane);
         b = os.get(w + 1, lane);
-        if (!(b <= e || a < e)) return false;
+        // A run of windows without tiles is jumped 32 offsets at a time (nobody has to visit them:
+        // all CTAs zero-fill them at start): the next window with tiles is the one before the
+        // first offset above `a`.
+        while (b == a) {
+            const int64_t idx = os.base + lane;
+            const unsigned m = __ballot_sync(0xffffffffu, idx > w && idx <= W && os.cur > a);
+            if (m) {
+                w = os.base + (__ffs(m) - 1) - 1;
+                b = os.get(w + 1, lane);
+            } else if (os.base + 32 <= W) {
+                w = os.base + 31;                   // offsets up to base + 31 all equal `a`
+                (void)os.get(os.base + 32, lane);   // slide the register window
+            } else {
+                w = W;
+                return false;
+            }
+        }
+        // Windows without tiles need no owner (all CTAs zero-fill them at start), so the walk ends at
+        // the first window that starts at or behind the range end: a run of empty windows there
+        // (padded blocks) would otherwise cost hundreds of cycles each on this dependent chain.
+        if (a >= e) return false;
         seg_s = a > s ? a : s;
         seg_e = b < e ? b : e;
         ++w;
@@ -456,9 +476,28 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
             uint32_t ai = 0;
             bool ok = true;
             long long w_af = 0;
+            // Windows without tiles produce zero rows.  They are dealt to all CTAs here, while the
+            // pipeline fills, instead of being written by whichever CTA's tile range they border:
+            // a run of empty windows (padded blocks, isolated nodes) would serialise on that one CTA.
+            if (!(prm.skip & 4)) {
+                for (int64_t w0 = blockIdx.x; w0 < W; w0 += gridDim.x) {
+                    if (__ldg(prm.window_offset + w0) != __ldg(prm.window_offset + w0 + 1)) continue;
+#pragma unroll
+                    for (int h = 0; h < NH; ++h) {
+                        const int64_t o0 = (w0 * TILE_ROWS) * prm.ldc + h * SLAB + 32 * q + lane;
+#pragma unroll
+                        for (int r = 0; r < 16; ++r) {
+                            const int64_t o = o0 + r * prm.ldc;
+                            if (prm.c_dtype == GRWS_F32) static_cast<float *>(prm.C)[o] = 0.0f;
+                            else static_cast<uint16_t *>(prm.C)[o] = 0;
+                        }
+                    }
+                }
+            }
             while (ok && wk.next_segment(lane)) {
                 const int64_t w = wk.window();
                 const bool nonempty = wk.seg_e > wk.seg_s;
+                if (!nonempty) continue;                   // zero rows were written above
                 uint32_t v[NH][16];
                 if (nonempty) {
                     const uint32_t buf = ai % NACC, aph = (ai / NACC) & 1u;
