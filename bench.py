@@ -460,11 +460,12 @@ def run_secondary(args):
         extra["sampling_only_seeds_per_s"] = world * per_gpu * n_s / (time.perf_counter() - t0)
         # the same step with batch i+1 sampled on a side stream by a producer thread while batch i trains
         from graph_rws_b200.helper import train_epoch_node_sampling
-        n_p = 40
+        n_p = 20
         train_dev = train.to(device)
         for pipe in (False, True):
-            lo = rank * per_gpu * n_p
-            idx = train_dev[lo:lo + per_gpu * n_p]
+            # the same number of batches on every rank (the gradient all-reduce pairs them up):
+            # each rank takes its own stretch of the training split, wrapping around its end
+            idx = train_dev[(torch.arange(per_gpu * n_p, device=device) + rank * per_gpu * n_p) % train_dev.numel()]
             train_epoch_node_sampling(model, graph, x, y, idx[:per_gpu * 4], opt, sampler, batch_size=per_gpu, pipeline=pipe)
             barrier()
             t0 = time.perf_counter()
