@@ -106,6 +106,14 @@ def train_epoch_node_sampling(model, graph, features, labels, train_idx, optimiz
     starts = list(range(0, n, batch_size))
     if max_batches is not None:
         starts = starts[:max_batches]
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+        # the gradient all-reduce pairs the batches of all ranks up: unequal counts would leave the
+        # ranks with more batches waiting in a collective for ever, so refuse before the first one
+        cnt = torch.tensor([len(starts), -len(starts)], device=device)
+        dist.all_reduce(cnt, op=dist.ReduceOp.MAX)
+        if int(cnt[0]) != -int(cnt[1]):
+            raise RuntimeError(f"ranks hold different numbers of batches ({len(starts)} here, "
+                               f"{-int(cnt[1])}..{int(cnt[0])} overall): shard train_idx evenly")
     main_stream = torch.cuda.current_stream(device)
     total = torch.zeros((), device=device)
     model.train()
