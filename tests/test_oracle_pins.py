@@ -20,7 +20,7 @@ def test_csr_to_bcsr_matches_reference_output(oracle, path):
 
 
 def test_known_answer_3x3(oracle):
-    # 3x3 CSR run through the reference's csr_to_bcsr_cpu during the survey
+    # a 3x3 CSR matrix and what the reference's csr_to_bcsr_cpu returns for it
     wo, cols, vals = oracle.csr_to_bcsr(3, [0, 2, 3, 5], [0, 2, 1, 0, 2], [.5, .25, 1, .125, .75])
     assert wo.tolist() == [0, 1]
     assert cols.tolist() == [0, 1, 2, -1, -1, -1, -1, -1]
