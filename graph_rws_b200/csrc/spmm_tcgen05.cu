@@ -20,9 +20,15 @@
 // power-law window lengths do not matter); the pieces of a window cut by a range boundary go to
 // scratch as fp32 partial tiles and the CTA that finishes its piece last sums them in CTA order.
 //
+// Windows without tiles are zero-filled by all CTAs at the start and skipped by the window walk.
+//
 // Warp roles: 0-3 epilogue (TMEM -> registers -> global), 4 MMA issuer, 5 TMA producer for tile
-// values and column ids, 6.. gather producers (one per ring slot).  Every mbarrier wait is bounded: on time-out the
-// kernel raises the status word at the start of scratch and all roles drain and return.
+// values and column ids, 6.. gather producers (one per ring slot).  The role index is read from
+// lane 0 and every TMA copy / MMA is issued by one elected lane, which keeps descriptors and
+// barrier addresses in uniform registers (the roles are chains of dependent instructions on
+// single warps: their instruction count is what the kernel's run time follows).  Every mbarrier
+// wait is bounded: on time-out the kernel raises the status word at the start of scratch and all
+// roles drain and return.
 #include <cuda.h>      // CUtensorMap and the cuTensorMapEncodeTiled prototype (resolved at run time)
 #include <stdlib.h>
 
@@ -42,11 +48,10 @@ constexpr int STAGE_TILES = GRWS_TC5_STAGE_TILES;    // tiles per pipeline stage
 constexpr int STAGE_SLOTS = STAGE_TILES * TILE_COLS; // gathered rows per stage
 constexpr int MMAS_PER_STAGE = STAGE_TILES / 2;
 constexpr int SLAB = 128;                            // features per MMA (its M dimension)
-constexpr int CHUNKS = SLAB * 2 / 16;                // 16-byte pieces of a 128-feature row
 // A operand of one K-step (16 slots x 128 features), MN-major with the 128-byte swizzle: four
 // 1024-byte atoms [slot half][feature half], an atom holds 8 slots x 64 features, slot k at
 // k * 128 bytes, its 16-byte piece c stored at piece c ^ k.  A gathered row therefore lands as
-// two contiguous (permuted) 128-byte lines, which cp.async moves as whole lines.
+// two contiguous (permuted) 128-byte lines, which the TMA gather writes as whole lines.
 constexpr int A_ATOM_BYTES = 1024;
 constexpr int A_LBO = A_ATOM_BYTES;                  // between the two 64-feature halves
 constexpr int A_SBO = 2 * A_ATOM_BYTES;              // between the two 8-slot halves
@@ -60,12 +65,12 @@ constexpr int META_BYTES = META_TILE_BYTES + META_COL_BYTES + META_CMD_BYTES;
 // bit 10 end of this CTA's work
 constexpr uint32_t CMD_COUNT = 31u, CMD_FIRST = 1u << 8, CMD_LAST = 1u << 9, CMD_END = 1u << 10;
 static_assert(STAGE_TILES <= (int)CMD_COUNT && STAGE_TILES % 2 == 0, "tile count field of the command word");
-constexpr int NACC = 4;                              // accumulator buffers in tensor memory
+#ifndef GRWS_TC5_NACC
+#define GRWS_TC5_NACC 4
+#endif
+constexpr int NACC = GRWS_TC5_NACC;                              // accumulator buffers in tensor memory
 #ifndef GRWS_TC5_PRODUCER_WARPS
 #define GRWS_TC5_PRODUCER_WARPS 5
-#endif
-#ifndef GRWS_TC5_NO_ELECT
-#define GRWS_TC5_ELECT 1     // TMA copies and MMAs are issued by one elected lane with warp-uniform operands
 #endif
 constexpr int NUM_PRODUCER_WARPS = GRWS_TC5_PRODUCER_WARPS;   // a multiple of the stage count
 constexpr int NUM_EPILOGUE = 128;
@@ -178,14 +183,6 @@ template <bool PROF> __device__ __forceinline__ void prof_mark(long long *dbg, u
 template <bool PROF> __device__ __forceinline__ long long prof_clock() {
     if constexpr (PROF) return clock64(); else return 0;
 }
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, uint32_t src_bytes, uint64_t pol) {
-    asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2, %3;"
-                 ::"r"(dst), "l"(src), "r"(src_bytes), "l"(pol) : "memory");
-}
-__device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
-    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar, uint64_t pol) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
                  ::"r"(dst), "l"(src), "r"(bytes), "r"(bar), "l"(pol) : "memory");
@@ -428,12 +425,8 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
                         fence_async_smem();
                         __syncwarp();
                     }
-#ifdef GRWS_TC5_ELECT
                     __syncwarp();
                     if (elect_one()) {
-#else
-                    if (lane == 0) {
-#endif
                         if (ok) {
                             const uint32_t bar = smem_u32(&ss->full_m[slot]);
                             uint8_t *dst = ring_m + (size_t)slot * META_BYTES;
@@ -480,16 +473,25 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
             // pipeline fills, instead of being written by whichever CTA's tile range they border:
             // a run of empty windows (padded blocks, isolated nodes) would serialise on that one CTA.
             if (!(prm.skip & 4)) {
-                for (int64_t w0 = blockIdx.x; w0 < W; w0 += gridDim.x) {
-                    if (__ldg(prm.window_offset + w0) != __ldg(prm.window_offset + w0 + 1)) continue;
+                // this CTA's share: a contiguous run of windows, 32 offsets per (coalesced) load
+                const int64_t per = (W + gridDim.x - 1) / gridDim.x;
+                const int64_t w_lo = (int64_t)blockIdx.x * per, w_hi = min(W, w_lo + per);
+                for (int64_t wb = w_lo; wb < w_hi; wb += 32) {
+                    const int64_t wl = wb + lane;
+                    const bool empty = wl < w_hi && __ldg(prm.window_offset + wl) == __ldg(prm.window_offset + wl + 1);
+                    unsigned m = __ballot_sync(0xffffffffu, empty);
+                    while (m) {
+                        const int64_t w0 = wb + (__ffs(m) - 1);
+                        m &= m - 1;
 #pragma unroll
-                    for (int h = 0; h < NH; ++h) {
-                        const int64_t o0 = (w0 * TILE_ROWS) * prm.ldc + h * SLAB + 32 * q + lane;
+                        for (int h = 0; h < NH; ++h) {
+                            const int64_t o0 = (w0 * TILE_ROWS) * prm.ldc + h * SLAB + 32 * q + lane;
 #pragma unroll
-                        for (int r = 0; r < 16; ++r) {
-                            const int64_t o = o0 + r * prm.ldc;
-                            if (prm.c_dtype == GRWS_F32) static_cast<float *>(prm.C)[o] = 0.0f;
-                            else static_cast<uint16_t *>(prm.C)[o] = 0;
+                            for (int r = 0; r < 16; ++r) {
+                                const int64_t o = o0 + r * prm.ldc;
+                                if (prm.c_dtype == GRWS_F32) static_cast<float *>(prm.C)[o] = 0.0f;
+                                else static_cast<uint16_t *>(prm.C)[o] = 0;
+                            }
                         }
                     }
                 }
@@ -591,31 +593,23 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
         }
     } else if (warp >= PRODUCER_WARP0) {
         // ------------------------------------------------------------------ gather producers
-        // Several warps per pipeline stage: producer warps k*w .. k*w+k-1 own gather slot w and fill
-        // every kStages-th stage, so the barrier polls and column-id reads of kStages stages overlap.
-        // The rows are fetched by the TMA unit (tile::gather4): a lane issues the copy of four
-        // consecutive slots x 64 features.  One warp issues a gather4 about every 220 cycles
-        // whatever the load (copies of different lanes go one after the other), while different
-        // warps issue in parallel, so a stage's 32 copies are spread over the warps of its slot.
-        // The copies complete on the stage's barrier.
+        // Producer warps k*w .. k*w+k-1 own ring slot w (k = 1 by default) and fill every kStages-th
+        // stage, so the barrier polls and column-id reads of kStages stages overlap.  The rows are
+        // fetched by the TMA unit (tile::gather4: four consecutive slots x 64 features per copy,
+        // 32 copies per stage and slab), all issued by one elected lane in an unrolled loop: a copy
+        // issued per lane costs its warp ~220 cycles (the copies of different lanes go one after
+        // the other and each marshals its operands into uniform registers), a copy from the elected
+        // lane with warp-uniform operands ~70.  The copies complete on the stage's barrier.
         constexpr int WARPS_PER_SLOT = NUM_PRODUCER_WARPS / Cfg<NH>::kStages;
         constexpr int STAGE_OPS = MMAS_PER_STAGE * 8;                          // gather4 copies per stage and slab
         static_assert(WARPS_PER_SLOT >= 1 && WARPS_PER_SLOT * Cfg<NH>::kStages == NUM_PRODUCER_WARPS, "producer warps per slot");
-        static_assert((STAGE_OPS + WARPS_PER_SLOT - 1) / WARPS_PER_SLOT <= 32, "one copy per lane");
         const uint64_t keep = policy_keep();
         const int pwarp = warp - PRODUCER_WARP0;
-        const int member = pwarp % WARPS_PER_SLOT;
-        // the copies of a stage are dealt round-robin to the warps of its slot, one per lane
-        const int op = member + lane * WARPS_PER_SLOT;        // (K-step, slot group, feature half) of this lane's copy
-        const bool issuer = op < STAGE_OPS;
-        const int opc = issuer ? op : 0;                      // idle lanes compute in-range addresses, they copy nothing
-        const int m = opc >> 3, grp = (opc >> 1) & 3, half = opc & 1;
-        // slots 4*grp .. 4*grp+3 of K-step m: slot half grp / 2, lines (4*grp) % 8 .. +3 of the atom
-        const uint32_t lane_off = (uint32_t)(m * NH * A_MMA_BYTES + (grp >> 1) * A_SBO + half * A_LBO + ((4 * grp) & 7) * 128);
+        const int member = pwarp % WARPS_PER_SLOT;            // the copies of a stage are dealt round-robin to the slot's warps
         long long w_full_m = 0, w_empty_g = 0;
         const uint32_t gs = (uint32_t)(pwarp / WARPS_PER_SLOT);
         const uint32_t full_bar = smem_u32(&ss->full_g[gs]), empty_bar = smem_u32(&ss->empty_g[gs]);
-        const uint32_t dst = smem_u32(ring_g + (size_t)gs * C::kStageBytes) + lane_off;
+        const uint32_t dst_slot = smem_u32(ring_g + (size_t)gs * C::kStageBytes);
         uint32_t gph = 0;
         for (uint32_t it = gs;; it += C::kStages, gph ^= 1u) {
             const uint32_t ms = it % C::kMeta, mph = (it / C::kMeta) & 1u;
@@ -631,10 +625,6 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
             const int ntiles = end ? 0 : (int)(cmd & CMD_COUNT);
             const int nvalid = ntiles * TILE_COLS;               // slots that carry a column id
             const int nmma = (ntiles + 1) >> 1;
-            // the four column ids of this lane's slots (slots past the last tile read nothing)
-            const int slot0 = 16 * m + 4 * grp;
-            int4 c = *reinterpret_cast<const int4 *>(meta + META_TILE_BYTES + slot0 * 4);
-            if (slot0 >= nvalid) c = make_int4(-1, -1, -1, -1);
             // the gather slot has been released by the MMA warp (it finished stage it - kStages)
             if (lane == 0) ok = mbar_wait_t<PROF>(empty_bar, gph ^ 1u, abort_flag, w_empty_g, 2);
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
@@ -651,12 +641,12 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
                 if (prm.skip & 2) mbar_arrive(full_bar);          // experiment: no gathers, nothing to wait for
                 else mbar_expect_tx(full_bar, (uint32_t)(nmma * 16 * SLAB * 2 * NH));
             }
-#ifdef GRWS_TC5_ELECT
-            // one elected lane issues all of this warp's copies: its operands are uniform but the row ids
+            // (K-step om, slot group og, feature half oh) of copy o: slots 4*og .. 4*og+3 of K-step om
+            // land in slot half og / 2, lines (4*og) % 8 .. +3 of the atom; slots past the last tile
+            // carry no column id and fetch row -1, which is out of bounds and reads zeros
             __syncwarp();
             if (elect_one() && !(prm.skip & 2)) {
                 constexpr int MAX_OPS = (STAGE_OPS + WARPS_PER_SLOT - 1) / WARPS_PER_SLOT;
-                const uint32_t dst_slot = smem_u32(ring_g + (size_t)gs * C::kStageBytes);
 #pragma unroll
                 for (int j = 0; j < MAX_OPS; ++j) {
                     const int o = member + j * WARPS_PER_SLOT;
@@ -673,24 +663,12 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
                 }
             }
             __syncwarp();
-            (void)issuer; (void)c; (void)dst; (void)half; (void)m;
-#else
-            if (issuer && m < nmma && !(prm.skip & 2)) {
-#pragma unroll
-                for (int h = 0; h < NH; ++h)
-                    tma_gather4(dst + (uint32_t)(h * A_MMA_BYTES), &b_map, full_bar, h * SLAB + half * 64, c.x, c.y, c.z, c.w, keep);
-            }
-#endif
             if (lane == 0) prof_mark<PROF>(prm.dbg, it, 3);
         }
         if (PROF && prm.dbg && threadIdx.x == PRODUCER_WARP0 * 32) { prm.dbg[blockIdx.x * 16 + 2] = w_full_m; prm.dbg[blockIdx.x * 16 + 3] = w_empty_g; }
     } else if (warp == MMA_WARP) {
         // ------------------------------------------------------------------ MMA issuer (one thread)
-#ifdef GRWS_TC5_ELECT
         if (elect_one()) {
-#else
-        if (lane == 0) {
-#endif
             const uint32_t idesc = (1u << 4) | ((uint32_t)prm.is_bf16 << 7) | ((uint32_t)prm.is_bf16 << 10) |
                                    (1u << 15) | ((16u >> 3) << 17) | ((128u >> 4) << 24);
             // descriptors of stage 0 / meta slot 0; other stages add their byte offset >> 4 to the low word
