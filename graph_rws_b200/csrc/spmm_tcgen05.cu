@@ -348,6 +348,66 @@ __device__ __forceinline__ void raise(Params const &prm, SharedStorage *ss, int 
     atomicMax(prm.status, code);
 }
 
+// The two rare paths of the epilogue live in functions of their own (not inlined), so that their
+// registers do not count against the per-window path of the kernel.
+
+// Rows of the windows without tiles in this CTA's share of the window list (a contiguous run,
+// 32 offsets per coalesced load); warp quarter q writes features 32q .. 32q+31 of every slab.
+template <int NH>
+__device__ __noinline__ void zero_fill_empty_windows(const int64_t *__restrict__ window_offset, void *C, int64_t ldc, int c_dtype,
+                                                    int64_t W, int q, int lane) {
+    const int64_t per = (W + gridDim.x - 1) / gridDim.x;
+    const int64_t w_lo = (int64_t)blockIdx.x * per, w_hi = min(W, w_lo + per);
+    for (int64_t wb = w_lo; wb < w_hi; wb += 32) {
+        const int64_t wl = wb + lane;
+        const bool empty = wl < w_hi && __ldg(window_offset + wl) == __ldg(window_offset + wl + 1);
+        unsigned m = __ballot_sync(0xffffffffu, empty);
+        while (m) {
+            const int64_t w0 = wb + (__ffs(m) - 1);
+            m &= m - 1;
+#pragma unroll
+            for (int h = 0; h < NH; ++h) {
+                const int64_t o0 = (w0 * TILE_ROWS) * ldc + h * SLAB + 32 * q + lane;
+                for (int r = 0; r < 16; ++r) {
+                    const int64_t o = o0 + r * ldc;
+                    if (c_dtype == GRWS_F32) static_cast<float *>(C)[o] = 0.0f;
+                    else static_cast<uint16_t *>(C)[o] = 0;
+                }
+            }
+        }
+    }
+}
+
+// Sum of the pieces of split window w (held by CTAs k0 .. k_last, the first one in its tail slot,
+// the others in their head slots), in CTA order, written to the window's rows.
+template <int NH>
+__device__ __noinline__ void sum_pieces(const float *partial, int64_t N, void *C, int64_t ldc, int c_dtype, int64_t w, int64_t k0,
+                                       int64_t k_last, int q, int lane) {
+    __threadfence();
+    const int64_t elems = TILE_ROWS * N;
+#pragma unroll
+    for (int h = 0; h < NH; ++h) {
+        const int64_t f = h * SLAB + 32 * q + lane;
+        float acc[16];
+        const float *p0 = partial + (2 * k0 + 1) * elems + f;
+#pragma unroll
+        for (int r = 0; r < 16; ++r) acc[r] = __ldcg(p0 + (int64_t)r * N);
+        for (int64_t kq = k0 + 1; kq <= k_last; ++kq) {
+            const float *pq = partial + (2 * kq) * elems + f;
+#pragma unroll
+            for (int r = 0; r < 16; ++r) acc[r] += __ldcg(pq + (int64_t)r * N);
+        }
+        const int64_t base = (w * TILE_ROWS) * ldc + f;
+#pragma unroll
+        for (int r = 0; r < 16; ++r) {
+            const int64_t o = base + r * ldc;
+            if (c_dtype == GRWS_F32) static_cast<float *>(C)[o] = acc[r];
+            else if (c_dtype == GRWS_F16) static_cast<__half *>(C)[o] = __float2half_rn(acc[r]);
+            else static_cast<__nv_bfloat16 *>(C)[o] = __float2bfloat16_rn(acc[r]);
+        }
+    }
+}
+
 template <int NH, bool PROF>
 __global__ void __launch_bounds__(NUM_THREADS, Cfg<NH>::kCtasPerSm)
 spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
@@ -472,30 +532,7 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
             // Windows without tiles produce zero rows.  They are dealt to all CTAs here, while the
             // pipeline fills, instead of being written by whichever CTA's tile range they border:
             // a run of empty windows (padded blocks, isolated nodes) would serialise on that one CTA.
-            if (!(prm.skip & 4)) {
-                // this CTA's share: a contiguous run of windows, 32 offsets per (coalesced) load
-                const int64_t per = (W + gridDim.x - 1) / gridDim.x;
-                const int64_t w_lo = (int64_t)blockIdx.x * per, w_hi = min(W, w_lo + per);
-                for (int64_t wb = w_lo; wb < w_hi; wb += 32) {
-                    const int64_t wl = wb + lane;
-                    const bool empty = wl < w_hi && __ldg(prm.window_offset + wl) == __ldg(prm.window_offset + wl + 1);
-                    unsigned m = __ballot_sync(0xffffffffu, empty);
-                    while (m) {
-                        const int64_t w0 = wb + (__ffs(m) - 1);
-                        m &= m - 1;
-#pragma unroll
-                        for (int h = 0; h < NH; ++h) {
-                            const int64_t o0 = (w0 * TILE_ROWS) * prm.ldc + h * SLAB + 32 * q + lane;
-#pragma unroll
-                            for (int r = 0; r < 16; ++r) {
-                                const int64_t o = o0 + r * prm.ldc;
-                                if (prm.c_dtype == GRWS_F32) static_cast<float *>(prm.C)[o] = 0.0f;
-                                else static_cast<uint16_t *>(prm.C)[o] = 0;
-                            }
-                        }
-                    }
-                }
-            }
+            if (!(prm.skip & 4)) zero_fill_empty_windows<NH>(prm.window_offset, prm.C, prm.ldc, prm.c_dtype, W, q, lane);
             while (ok && wk.next_segment(lane)) {
                 const int64_t w = wk.window();
                 const bool nonempty = wk.seg_e > wk.seg_s;
@@ -562,31 +599,7 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
                         ss->last_piece = (old == (int)(k_last - k0)) ? 1 : 0;
                     }
                     asm volatile("bar.sync 1, 128;" ::: "memory");
-                    if (*reinterpret_cast<volatile int *>(&ss->last_piece)) {
-                        __threadfence();
-                        const int64_t elems = TILE_ROWS * prm.N;
-#pragma unroll
-                        for (int h = 0; h < NH; ++h) {
-                            const int64_t f = h * SLAB + 32 * q + lane;
-                            float acc[16];
-                            const float *p0 = prm.partial + (2 * k0 + 1) * elems + f;
-#pragma unroll
-                            for (int r = 0; r < 16; ++r) acc[r] = __ldcg(p0 + (int64_t)r * prm.N);
-                            for (int64_t kq = k0 + 1; kq <= k_last; ++kq) {
-                                const float *pq = prm.partial + (2 * kq) * elems + f;
-#pragma unroll
-                                for (int r = 0; r < 16; ++r) acc[r] += __ldcg(pq + (int64_t)r * prm.N);
-                            }
-                            const int64_t base = (w * TILE_ROWS) * prm.ldc + f;
-#pragma unroll
-                            for (int r = 0; r < 16; ++r) {
-                                const int64_t o = base + r * prm.ldc;
-                                if (prm.c_dtype == GRWS_F32) static_cast<float *>(prm.C)[o] = acc[r];
-                                else if (prm.c_dtype == GRWS_F16) static_cast<__half *>(prm.C)[o] = __float2half_rn(acc[r]);
-                                else static_cast<__nv_bfloat16 *>(prm.C)[o] = __float2bfloat16_rn(acc[r]);
-                            }
-                        }
-                    }
+                    if (*reinterpret_cast<volatile int *>(&ss->last_piece)) sum_pieces<NH>(prm.partial, prm.N, prm.C, prm.ldc, prm.c_dtype, w, k0, k_last, q, lane);
                 }
             }
             if (PROF && prm.dbg && threadIdx.x == EPILOGUE_WARP0 * 32) prm.dbg[blockIdx.x * 16 + 7] = w_af;
