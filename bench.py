@@ -258,7 +258,7 @@ def run_ours(args):
                          "algorithmic_bytes": bytes_fwd,
                          # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu capture
                          # summarised in profiles/spmm_tc5_kernel_spmm_mid.md (spmm_mid, tcgen05 kernel only)
-                         "traffic": 153.5e6 if (args.workload == "spmm_mid" and args.algo != "warp") else None},
+                         "traffic": 156.3e6 if (args.workload == "spmm_mid" and args.algo != "warp") else None},
             "e2e": {"value": world * bytes_step / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s",
                     "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": int(H_pin.numel() + G_pin.numel()) * esize,
