@@ -78,6 +78,56 @@ __device__ __forceinline__ int64_t warp_count_ends_le(const int64_t *__restrict_
     return lo;
 }
 
+// The same count for two values at once with a 128-ary search (four probes per lane): the two
+// searches' loads are all in flight together, so a pair of cuts costs two or three rounds of
+// memory latency instead of eight (W = 10^4 .. 10^6).  Every lane must call it with the same arguments.
+__device__ __forceinline__ void warp_count_ends_le_pair(const int64_t *__restrict__ window_offset, int64_t W,
+                                                        int64_t x0, int64_t x1, int lane, int64_t *r0, int64_t *r1) {
+    int64_t lo[2] = {0, 0}, hi[2] = {W, W};
+    const int64_t x[2] = {x0, x1};
+    while (hi[0] > lo[0] || hi[1] > lo[1]) {
+        int64_t step[2];
+        bool le[2][4];
+#pragma unroll
+        for (int s = 0; s < 2; ++s) {
+            step[s] = (hi[s] - lo[s] + 127) / 128;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int64_t probe = lo[s] + (int64_t)(lane * 4 + j) * step[s];
+                le[s][j] = (probe < hi[s]) && (__ldg(window_offset + probe + 1) <= x[s]);
+            }
+        }
+#pragma unroll
+        for (int s = 0; s < 2; ++s) {
+            int cnt = 0;                                      // ends are sorted: `le` is a prefix in probe order
+#pragma unroll
+            for (int j = 0; j < 4; ++j) cnt += __popc(__ballot_sync(0xffffffffu, le[s][j]));
+            const int64_t new_lo = (cnt == 0) ? lo[s] : min(hi[s], lo[s] + (int64_t)(cnt - 1) * step[s] + 1);
+            const int64_t new_hi = (cnt == 128) ? hi[s] : min(hi[s], lo[s] + (int64_t)cnt * step[s]);
+            lo[s] = new_lo;
+            hi[s] = new_hi;
+        }
+    }
+    *r0 = lo[0];
+    *r1 = lo[1];
+}
+
+// cut positions of boundaries k and k + 1 at once (see warp_cut below for one boundary)
+__device__ __forceinline__ void warp_cut_pair(const int64_t *__restrict__ window_offset, int64_t W, int64_t T,
+                                              int64_t k, int64_t n_items, int64_t chunk, int64_t long_window,
+                                              int lane, int64_t *s_out, int64_t *e_out, int64_t *w_first) {
+    const int64_t xs = k * chunk, xe = (k + 1) * chunk;
+    const bool s_end = k >= n_items || xs >= T, e_end = k + 1 >= n_items || xe >= T;
+    int64_t ws, we;
+    warp_count_ends_le_pair(window_offset, W, s_end ? 0 : xs, e_end ? 0 : xe, lane, &ws, &we);   // window containing the tile
+    // (a boundary at or behind the last tile loads nothing: its window index may be W)
+    const int64_t as = s_end ? 0 : __ldg(window_offset + ws), bs = s_end ? 0 : __ldg(window_offset + ws + 1);
+    const int64_t ae = e_end ? 0 : __ldg(window_offset + we), be = e_end ? 0 : __ldg(window_offset + we + 1);
+    *s_out = s_end ? T : ((bs - as <= long_window) ? as : xs);
+    *e_out = e_end ? T : ((be - ae <= long_window) ? ae : xe);
+    *w_first = s_end ? W : ws;
+}
+
 struct ItemRange {
     int64_t s, e;      // tile range [s, e)
     int64_t w_lo;      // first window owned (or touched) by this item

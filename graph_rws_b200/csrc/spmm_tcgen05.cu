@@ -454,9 +454,8 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
         // a cut inside a window of at most chunk/16 tiles moves back to that window's start, so
         // only long windows are ever split between CTAs (tile counts stay balanced within chunk >> lw_shift)
         const int64_t long_window = chunk >> prm.lw_shift;
-        int64_t w_first, w_unused;
-        const int64_t s = warp_cut(prm.window_offset, W, T, blockIdx.x, G, chunk, long_window, lane, &w_first);
-        const int64_t e = warp_cut(prm.window_offset, W, T, (int64_t)blockIdx.x + 1, G, chunk, long_window, lane, &w_unused);
+        int64_t w_first, s, e;
+        warp_cut_pair(prm.window_offset, W, T, blockIdx.x, G, chunk, long_window, lane, &s, &e, &w_first);
         Walker wk;
         wk.init(prm.window_offset, W, s, e, blockIdx.x == 0 ? 0 : w_first, lane);
 
