@@ -121,8 +121,15 @@ def spmm_tc(window_offset, original_col_indices, values_condensed, input_B, warp
 # ---------------------------------------------------------------------------------------------
 # CSR -> BCSR and the cached transposed BCSR
 # ---------------------------------------------------------------------------------------------
-def csr_to_bcsr(num_rows, row_ptr, col_idx, values, tile_rows=16, tile_cols=8, values_dtype=torch.float32):
-    """Device builder: CUDA tensors in, CUDA tensors out (window_offset, cols, vals)."""
+def csr_to_bcsr(num_rows, row_ptr, col_idx, values, tile_rows=16, tile_cols=8, values_dtype=torch.float32,
+                exact=True):
+    """Device builder: CUDA tensors in, CUDA tensors out (window_offset, cols, vals).
+
+    With ``exact`` the tile count is read back from the device to size ``cols`` / ``vals`` exactly
+    (what the reference's builder returns).  ``exact=False`` skips that host synchronisation and
+    sizes them by the bound ``entries / 8 + windows`` (every window wastes less than one tile): the
+    arrays then end in unused tiles (column ids -1, values 0) which no kernel visits, since all of
+    them walk ``window_offset``.  Per-step builders (sampled blocks, their transposes) use it."""
     if tile_rows != 16 or tile_cols != 8:
         raise RuntimeError("Currently only supports tile 16x8")
     lib = _native.lib()
@@ -137,7 +144,7 @@ def csr_to_bcsr(num_rows, row_ptr, col_idx, values, tile_rows=16, tile_cols=8, v
     st = _stream(dev)
     _native.check(lib.grws_csr_to_bcsr_count(num_rows, _ptr(row_ptr), _ptr(col_idx), _ptr(values), nnz,
                                              wo.data_ptr(), scratch.data_ptr(), scratch.numel(), st))
-    T = int(wo[-1].item())
+    T = int(wo[-1].item()) if exact else nnz // 8 + W
     cols = torch.empty(T * 8, dtype=torch.int32, device=dev)
     vals = torch.empty(T * 128, dtype=values_dtype, device=dev)
     _native.check(lib.grws_csr_to_bcsr_fill(num_rows, nnz, wo.data_ptr(), T, _ptr(cols), _ptr(vals),
@@ -156,8 +163,9 @@ def csr_to_bcsr_cpu(num_rows, row_ptr, col_idx, values, tile_rows, tile_cols):
     return wo.cpu(), cols.cpu(), vals.cpu()
 
 
-def bcsr_transpose(window_offset, cols, vals, num_cols, values_dtype=None):
-    """BCSR of A^T (rows = column ids of A, ``num_cols`` of them; columns = rows of A)."""
+def bcsr_transpose(window_offset, cols, vals, num_cols, values_dtype=None, exact=True):
+    """BCSR of A^T (rows = column ids of A, ``num_cols`` of them; columns = rows of A).
+    ``exact`` as in ``csr_to_bcsr``."""
     lib = _native.lib()
     dev = vals.device
     W = window_offset.shape[0] - 1
@@ -173,7 +181,7 @@ def bcsr_transpose(window_offset, cols, vals, num_cols, values_dtype=None):
     _native.check(lib.grws_bcsr_transpose_fill(_ptr(window_offset), _ptr(cols), _ptr(vals), _DT[vals.dtype],
                                                W, num_cols, row_ptr_t.data_ptr(), _ptr(col_t), _ptr(val_t),
                                                scratch.data_ptr(), scratch.numel(), st))
-    return csr_to_bcsr(num_cols, row_ptr_t, col_t, val_t, values_dtype=values_dtype or vals.dtype)
+    return csr_to_bcsr(num_cols, row_ptr_t, col_t, val_t, values_dtype=values_dtype or vals.dtype, exact=exact)
 
 
 class _TransposeCache:

@@ -54,11 +54,12 @@ def sample_hop(row_ptr, col_idx, values, nodes, fanout, seed=DEFAULT_SEED, hop=0
     return nbr, w, cnt
 
 
-def build_block(dst, nbr, w, values_dtype=torch.float32, _marks=None):
+def build_block(dst, nbr, w, values_dtype=torch.float32, _marks=None, exact=True):
     """Dedup + reindex + BCSR build of one hop.
 
     Returns (src i32 [n_src], window_offset, cols, vals): rows are the ``dst`` nodes in order,
-    columns are positions in ``src`` = dst ++ ascending new nodes."""
+    columns are positions in ``src`` = dst ++ ascending new nodes.  ``exact=False`` saves the
+    read-back of the tile count (see ``csr_to_bcsr``): cols / vals then end in unused tiles."""
     from . import csr_to_bcsr
     lib = _native.lib()
     dev = dst.device
@@ -80,7 +81,7 @@ def build_block(dst, nbr, w, values_dtype=torch.float32, _marks=None):
     val = torch.empty(n_edges, dtype=torch.float32, device=dev)
     _native.check(lib.grws_block_compact(_ptr(local), _ptr(w), n_dst, fanout, row_ptr.data_ptr(), _ptr(col),
                                          _ptr(val), st))
-    wo, cols, vals = csr_to_bcsr(n_dst, row_ptr, col, val, values_dtype=values_dtype)
+    wo, cols, vals = csr_to_bcsr(n_dst, row_ptr, col, val, values_dtype=values_dtype, exact=exact)
     return src[:n_src], wo, cols, vals
 
 
@@ -105,7 +106,7 @@ class SamplingTimingResult:
 
 
 def sample_layers_csr(row_ptr, col_idx, values, seeds, fanouts, seed=DEFAULT_SEED, values_dtype=torch.float32,
-                      timing=False, pad_to=0):
+                      timing=False, pad_to=0, exact=True):
     """Multi-hop sampling over a CSR graph.  ``fanouts`` are consumed in the order given (the caller
     passes them output layer first, like sampler/sampler.py:202-204).  Returns one
     [window_offset, cols, vals, dst_nodes, src_nodes] list per hop and one timing object per hop.
@@ -123,7 +124,7 @@ def sample_layers_csr(row_ptr, col_idx, values, seeds, fanouts, seed=DEFAULT_SEE
             torch.cuda.synchronize(dev)
         t1 = time.perf_counter()
         marks = []
-        src, wo, cols, vals = build_block(dst, nbr, w, values_dtype=values_dtype, _marks=marks)
+        src, wo, cols, vals = build_block(dst, nbr, w, values_dtype=values_dtype, _marks=marks, exact=exact)
         t3 = time.perf_counter()
         if pad_to > 0 and src.numel() % pad_to:
             pad = pad_to - src.numel() % pad_to

@@ -249,7 +249,9 @@ template <int DT, int NG>
 __global__ void __launch_bounds__(WARPS_PER_CTA * 32)
 spmm_warp_kernel(const SpmmWarpParams prm) {
     using G = StepGeom<DT>;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    // the warp index is read from lane 0 so that the compiler knows it (and the work item, window and tile
+    // indices derived from it) to be the same in all lanes and can keep them in uniform registers
+    const int lane = threadIdx.x & 31, warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0);
     const int g = lane >> 2, t = lane & 3;
     const int64_t item = (int64_t)blockIdx.x * WARPS_PER_CTA + warp;
     if (item >= prm.n_items) return;

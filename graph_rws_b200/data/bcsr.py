@@ -92,7 +92,8 @@ class BCSRGraph:
         if hit is not None and hit[0] == self._versions():
             return hit[1]
         wo, cols, vals = bcsr_transpose(self.window_offset, self.original_col_indices,
-                                        self.values_condensed, n, values_dtype=dtype)
+                                        self.values_condensed, n, values_dtype=dtype,
+                                        exact=not getattr(self, 'transient', False))
         gt = BCSRGraph(num_nodes=n, num_edges=None, tile_rows=self.tile_rows, tile_cols=self.tile_cols,
                        window_offset=wo, original_col_indices=cols, values_condensed=vals,
                        device=vals.device, num_rows=n, num_cols=self.num_windows * self.tile_rows,

@@ -89,7 +89,7 @@ class BCSRSampler:
         hops, timing_list = core.sample_layers_csr(row_ptr, col_idx, values, seed_nodes, reversed_fanouts,
                                                    seed=self.seed + self.step,
                                                    values_dtype=g.values_condensed.dtype, timing=self.verbose,
-                                                   pad_to=self.pad_to)
+                                                   pad_to=self.pad_to, exact=False)
         if self.verbose:
             num_layers = len(self.fanouts)
             for i, t in enumerate(timing_list):
@@ -106,6 +106,7 @@ class BCSRSampler:
                                             tile_rows=self.tile_rows, tile_cols=self.tile_cols, device=wo.device)
             sub.output_nodes = dst          # global ids of the block's rows
             sub.input_nodes = src           # global ids of the block's columns; starts with output_nodes
+            sub.transient = True            # lives for one step: its arrays and its transposed graph skip exact sizing
             layers.insert(0, sub)           # keep input -> output order
         return layers
 

@@ -114,7 +114,9 @@ int grws_spmm_fwd_static(const int64_t *window_offset, const int32_t *cols, cons
  * the last duplicate of a (row, column) pair winning.
  *   count: writes window_offset [ceil(num_rows/16)+1]; the caller then reads its last entry
  *          (the tile count T) and allocates out_cols [T*8], out_vals [T*128];
- *   fill : must get the same scratch buffer, untouched since the count call.
+ *   fill : must get the same scratch buffer, untouched since the count call.  num_tiles may be
+ *          any bound >= T (nnz / 8 + number of windows always is), which saves the caller the
+ *          read-back: the tiles past T are written empty (ids -1, values 0).
  * row_ptr int64 [num_rows+1], col_idx int32 [nnz] (0 <= id), values fp32 [nnz]; nnz < 2^31.
  * ------------------------------------------------------------------------------------------ */
 size_t grws_csr_to_bcsr_scratch_bytes(int64_t num_rows, int64_t nnz);
