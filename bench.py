@@ -288,6 +288,7 @@ def cpu_baseline(workload, csr, H_host, G_host, budget_s=12.0):
     transposed product of the same workload, repeated until about `budget_s` seconds have passed."""
     import oracle
     from graph_rws_b200.data import synthetic
+    oracle.use_all_host_threads()
     wo, cols, vals = oracle.csr_to_bcsr(csr.num_nodes, csr.row_ptr, csr.col_idx, csr.values)
     vals = H_host.new_tensor(vals).float().numpy()          # rounded to the storage dtype like the GPU copy
     B, G = H_host.float().numpy(), G_host.float().numpy()
@@ -314,6 +315,7 @@ def run_reference(args):
     import torch
     import oracle
     from graph_rws_b200.data import synthetic
+    oracle.use_all_host_threads()          # torchrun exports OMP_NUM_THREADS=1
     cfg, width, dt = WORKLOADS[args.workload]
     csr = synthetic.graph_for_config(cfg)
     dtype = {"f16": torch.float16, "bf16": torch.bfloat16, "f32": torch.float32}[dt]

@@ -52,6 +52,15 @@ def num_threads() -> int:
     return int(lib().grws_oracle_num_threads())
 
 
+def use_all_host_threads() -> int:
+    """OpenMP thread count := the cores this process may run on (a launcher may have exported
+    OMP_NUM_THREADS=1); returns the count."""
+    import os
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    lib().grws_oracle_set_num_threads(ctypes.c_int(n))
+    return num_threads()
+
+
 def csr_to_bcsr(num_rows, row_ptr, col_idx, values, tile_rows=16, tile_cols=8):
     """CSR -> (window_offset i64, original_col_indices i32, values_condensed f32).
 

@@ -53,6 +53,16 @@ static int64_t lower_bound_i32(const int32_t *v, int64_t n, int32_t key) {
     return lo;
 }
 
+/* Launchers such as torchrun export OMP_NUM_THREADS=1; a caller that wants the host's cores for a
+ * timed CPU run sets the count itself. */
+API void grws_oracle_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 API int grws_oracle_num_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();
@@ -174,8 +184,10 @@ API void grws_oracle_spmm_transpose(int64_t W, int64_t F, int64_t tile_rows, int
                                     const float *vals, const float *grad_out, int64_t num_cols,
                                     float *grad_in) {
     double *acc = (double *)calloc((size_t)(num_cols * F), sizeof(double));
-    /* threads split the feature range, so every output element is summed by one thread in the
-     * same (window, tile, row, slot) order: parallel and still deterministic */
+    /* threads own contiguous ranges of output rows (column ids of A): every thread scans all column
+     * ids and adds only the entries of its own rows, so every output element is summed by one
+     * thread in (window, tile, row) order: parallel over all features at once, no atomics, and the
+     * same result for any thread count */
 #pragma omp parallel
     {
 #ifdef _OPENMP
@@ -183,22 +195,28 @@ API void grws_oracle_spmm_transpose(int64_t W, int64_t F, int64_t tile_rows, int
 #else
         const int nt = 1, tid = 0;
 #endif
-        const int64_t f0 = F * tid / nt, f1 = F * (tid + 1) / nt;
-        if (f1 > f0)
+        const int64_t c0 = num_cols * tid / nt, c1 = num_cols * (tid + 1) / nt;
+        if (c1 > c0)
             for (int64_t w = 0; w < W; ++w)
-                for (int64_t t = window_offset[w]; t < window_offset[w + 1]; ++t)
+                for (int64_t t = window_offset[w]; t < window_offset[w + 1]; ++t) {
+                    const int32_t *tc = cols + t * tile_cols;
+                    int any = 0;
+                    for (int64_t c = 0; c < tile_cols; ++c) any |= (tc[c] >= c0 && tc[c] < c1);
+                    if (!any) continue;
                     for (int64_t r = 0; r < tile_rows; ++r) {
                         const float *g = grad_out + (w * tile_rows + r) * F;
                         for (int64_t c = 0; c < tile_cols; ++c) {
-                            int32_t col = cols[t * tile_cols + c];
-                            if (col == -1) continue;
+                            int32_t col = tc[c];
+                            if (col < c0 || col >= c1) continue;        /* -1 is in nobody's range */
                             float a = vals[t * tile_rows * tile_cols + r * tile_cols + c];
                             if (a == 0.0f) continue;
                             double *o = acc + (int64_t)col * F;
-                            for (int64_t f = f0; f < f1; ++f) o[f] += (double)a * (double)g[f];
+                            for (int64_t f = 0; f < F; ++f) o[f] += (double)a * (double)g[f];
                         }
                     }
+                }
     }
+#pragma omp parallel for schedule(static)
     for (int64_t i = 0; i < num_cols * F; ++i) grad_in[i] = (float)acc[i];
     free(acc);
 }
