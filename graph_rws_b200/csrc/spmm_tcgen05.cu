@@ -63,8 +63,22 @@ constexpr int META_CMD_BYTES = 16;                   // per-stage command word w
 constexpr int META_BYTES = META_TILE_BYTES + META_COL_BYTES + META_CMD_BYTES;
 // command word: bits 0-4 tile count, bit 8 first stage of a window segment, bit 9 last stage,
 // bit 10 end of this CTA's work
+#ifndef GRWS_TC5_SPAN
+#define GRWS_TC5_SPAN 0
+#endif
+#if GRWS_TC5_SPAN
+// Stages that span windows: a stage is MMAS_PER_STAGE K-steps (tile pairs), each of which belongs
+// to one window segment.  Command word: bits 0-2 number of K-steps, bits 4+3i .. 6+3i the flags of
+// K-step i (first of its segment, last of its segment, second tile absent), bit 31 end of work.
+constexpr uint32_t CMD_COUNT = 7u, CMD_END = 1u << 31;
+constexpr uint32_t KS_FIRST = 1u, KS_LAST = 2u, KS_SINGLE = 4u;
+__device__ __forceinline__ uint32_t kstep_flags(uint32_t cmd, int i) { return (cmd >> (4 + 3 * i)) & 7u; }
+constexpr uint32_t CMD_FIRST = 0, CMD_LAST = 0;      // unused in this mode
+#else
 constexpr uint32_t CMD_COUNT = 31u, CMD_FIRST = 1u << 8, CMD_LAST = 1u << 9, CMD_END = 1u << 10;
-static_assert(STAGE_TILES <= (int)CMD_COUNT && STAGE_TILES % 2 == 0, "tile count field of the command word");
+#endif
+static_assert((GRWS_TC5_SPAN ? MMAS_PER_STAGE : STAGE_TILES) <= (int)CMD_COUNT && STAGE_TILES % 2 == 0, "count field of the command word");
+static_assert(!GRWS_TC5_SPAN || MMAS_PER_STAGE <= 9, "K-step flags of the command word");
 #ifndef GRWS_TC5_NACC
 #define GRWS_TC5_NACC 4
 #endif
@@ -120,6 +134,10 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 }
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// adds to the bytes the current phase waits for, without arriving
+__device__ __forceinline__ void mbar_expect_tx_only(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
@@ -469,6 +487,70 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
             bool ok = true;
             long long w_empty_m = 0;
             const long long t_start = prof_clock<PROF>();
+#if GRWS_TC5_SPAN
+            static_assert(NUM_META_WARPS == 1, "stages that span windows are packed by one warp");
+            // K-steps are packed into stages across window segments; a stage is published (command
+            // word written, barrier arrived on) when it is full or the CTA's range ends
+            uint32_t cmdw = 0, slot = 0;
+            int stage_k = 0;
+            while (ok && wk.next_segment(lane)) {
+                int64_t t0 = wk.seg_s;
+                bool first = true;
+                while (ok && t0 < wk.seg_e) {
+                    if (stage_k == 0) {
+                        slot = it % C::kMeta;
+                        const uint32_t ph = (it / C::kMeta) & 1u;
+                        if (lane == 0) ok = mbar_wait_t<PROF>(smem_u32(&ss->empty_m[slot]), ph ^ 1u, abort_flag, w_empty_m, 5);
+                        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+                        if (!ok) { if (lane == 0) raise(prm, ss, ST_TIMEOUT_META); break; }
+                    }
+                    const int n = (int)min(wk.seg_e - t0, (int64_t)(MMAS_PER_STAGE - stage_k) * 2);    // tiles placed now
+                    const int ks = (n + 1) >> 1;
+                    uint8_t *dst = ring_m + (size_t)slot * META_BYTES;
+                    const uint32_t bar = smem_u32(&ss->full_m[slot]);
+                    if (n & 1) {        // the segment ends on a first tile: the K-step's second tile multiplies as zeros
+                        if (lane < 16)
+                            *reinterpret_cast<uint4 *>(dst + (size_t)(stage_k * 2 + n) * TILE_BYTES + lane * 16) = make_uint4(0u, 0u, 0u, 0u);
+                        fence_async_smem();
+                        __syncwarp();
+                    }
+                    // flags: the piece's first K-step opens the segment, its last one may close it
+                    cmdw |= (first ? KS_FIRST : 0u) << (4 + 3 * stage_k);
+                    cmdw |= ((t0 + n == wk.seg_e ? KS_LAST : 0u) | ((n & 1) ? KS_SINGLE : 0u)) << (4 + 3 * (stage_k + ks - 1));
+                    const bool full = stage_k + ks == MMAS_PER_STAGE;
+                    if (elect_one()) {
+                        if (!(prm.skip & 8)) {
+                            mbar_expect_tx_only(bar, (uint32_t)n * (TILE_BYTES + TILE_COLS * 4));
+                            bulk_g2s(smem_u32(dst + (size_t)stage_k * 2 * TILE_BYTES), static_cast<const uint8_t *>(prm.vals) + t0 * TILE_BYTES,
+                                     (uint32_t)n * TILE_BYTES, bar, pol);
+                            bulk_g2s(smem_u32(dst + META_TILE_BYTES + (size_t)stage_k * 2 * TILE_COLS * 4), prm.cols + t0 * TILE_COLS,
+                                     (uint32_t)n * TILE_COLS * 4, bar, pol);
+                        }
+                        if (full) {                                // publish the stage
+                            *reinterpret_cast<volatile uint32_t *>(dst + META_TILE_BYTES + META_COL_BYTES) = (uint32_t)MMAS_PER_STAGE | cmdw;
+                            mbar_arrive(bar);                      // release: publishes the command
+                            prof_mark<PROF>(prm.dbg, it, 0);
+                        }
+                    }
+                    stage_k += ks;
+                    t0 += n;
+                    first = false;
+                    if (full) {
+                        ++it;
+                        stage_k = 0;
+                        cmdw = 0;
+                    }
+                }
+            }
+            if (ok && stage_k > 0) {                               // the last, partly filled stage
+                __syncwarp();
+                if (elect_one()) {
+                    *reinterpret_cast<volatile uint32_t *>(ring_m + (size_t)slot * META_BYTES + META_TILE_BYTES + META_COL_BYTES) = (uint32_t)stage_k | cmdw;
+                    mbar_arrive(smem_u32(&ss->full_m[slot]));
+                }
+                ++it;
+            }
+#else
             while (ok && wk.next_segment(lane)) {
                 for (int64_t t0 = wk.seg_s; ok && t0 < wk.seg_e; t0 += STAGE_TILES, ++it) {
                     if (it % NUM_META_WARPS != meta_id) continue;      // another meta warp's stage
@@ -508,6 +590,7 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
                     ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
                 }
             }
+#endif
             if (lane == 0 && meta_id == 0) {   // one end marker per gather slot; the MMA warp stops at the first
                 for (int j = 0; ok && j < C::kStages; ++j, ++it) {
                     const uint32_t slot = it % C::kMeta, ph = (it / C::kMeta) & 1u;
@@ -634,9 +717,13 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
             const uint8_t *meta = ring_m + (size_t)ms * META_BYTES;
             const uint32_t cmd = *reinterpret_cast<const volatile uint32_t *>(meta + META_TILE_BYTES + META_COL_BYTES);
             const bool end = (cmd & CMD_END) != 0;
+#if GRWS_TC5_SPAN
+            const int nmma = end ? 0 : (int)(cmd & CMD_COUNT);   // K-steps of the stage
+#else
             const int ntiles = end ? 0 : (int)(cmd & CMD_COUNT);
             const int nvalid = ntiles * TILE_COLS;               // slots that carry a column id
             const int nmma = (ntiles + 1) >> 1;
+#endif
             // the gather slot has been released by the MMA warp (it finished stage it - kStages)
             if (lane == 0) ok = mbar_wait_t<PROF>(empty_bar, gph ^ 1u, abort_flag, w_empty_g, 2);
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
@@ -666,7 +753,11 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
                     if (o < STAGE_OPS && om < nmma) {
                         const int s0 = 16 * om + 4 * og;
                         int4 r = *reinterpret_cast<const int4 *>(meta + META_TILE_BYTES + s0 * 4);
+#if GRWS_TC5_SPAN
+                        if ((kstep_flags(cmd, om) & KS_SINGLE) && og >= 2) r = make_int4(-1, -1, -1, -1);
+#else
                         if (s0 >= nvalid) r = make_int4(-1, -1, -1, -1);
+#endif
                         const uint32_t off = (uint32_t)(om * NH * A_MMA_BYTES + (og >> 1) * A_SBO + oh * A_LBO + ((4 * og) & 7) * 128);
 #pragma unroll
                         for (int h = 0; h < NH; ++h)
@@ -699,6 +790,38 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
                 const uint32_t cmd = *reinterpret_cast<const volatile uint32_t *>(ring_m + ms * META_BYTES + META_TILE_BYTES + META_COL_BYTES);
                 if (cmd & CMD_END) break;
                 if (PROF) t_cmd += prof_clock<PROF>() - tc0 + (long long)(cmd & 0);
+#if GRWS_TC5_SPAN
+                const int nmma = (int)(cmd & CMD_COUNT);
+                const long long tf0 = prof_clock<PROF>();
+                tc_fence_after();
+                const long long ti0 = prof_clock<PROF>();
+                t_fence += ti0 - tf0;
+                const uint64_t ad = a_desc0 + (uint64_t)(gs * (C::kStageBytes >> 4));
+                const uint64_t bd = b_desc0 + (uint64_t)(ms * (META_BYTES >> 4));
+                bool alive = true;
+#pragma unroll
+                for (int m = 0; m < MMAS_PER_STAGE; ++m) {
+                    if (m < nmma && alive) {
+                        const uint32_t f = kstep_flags(cmd, m);
+                        if (f & KS_FIRST) {                 // a new window segment: the next accumulator buffer
+                            buf = ai % NACC;
+                            const uint32_t aph = (ai / NACC) & 1u;
+                            ++ai;
+                            if (!mbar_wait_t<PROF>(smem_u32(&ss->acc_empty[buf]), aph ^ 1u, abort_flag, w_acc)) { raise(prm, ss, ST_TIMEOUT_ACC); alive = false; }
+                            tc_fence_after();
+                        }
+                        if (alive && !(prm.skip & 1)) {
+                            const uint32_t d_tmem = tmem_base + buf * C::kAccCols;
+#pragma unroll
+                            for (int h = 0; h < NH; ++h)
+                                umma_f16(d_tmem + h * 16, ad + (uint64_t)(((m * NH + h) * A_MMA_BYTES) >> 4),
+                                         bd + (uint64_t)((m * 2 * TILE_BYTES) >> 4), idesc, (f & KS_FIRST) ? 0u : 1u);
+                        }
+                        if (alive && (f & KS_LAST)) umma_commit(smem_u32(&ss->acc_full[buf]));
+                    }
+                }
+                if (!alive) break;
+#else
                 const int nmma = (int)((cmd & CMD_COUNT) + 1u) >> 1;
                 if (cmd & CMD_FIRST) {
                     buf = ai % NACC;
@@ -726,9 +849,12 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
                                      bd + (uint64_t)((m * 2 * TILE_BYTES) >> 4), idesc, m > 0 ? 1u : first);
                     }
                 }
+#endif
                 const long long ti1 = prof_clock<PROF>();
                 umma_commit(smem_u32(&ss->empty_g[gs]));
+#if !GRWS_TC5_SPAN
                 if (cmd & CMD_LAST) umma_commit(smem_u32(&ss->acc_full[buf]));
+#endif
                 const long long ti2 = prof_clock<PROF>();
                 t_issue += ti1 - ti0;
                 t_commit += ti2 - ti1;
