@@ -798,29 +798,38 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
                 t_fence += ti0 - tf0;
                 const uint64_t ad = a_desc0 + (uint64_t)(gs * (C::kStageBytes >> 4));
                 const uint64_t bd = b_desc0 + (uint64_t)(ms * (META_BYTES >> 4));
+                // first pass: take the accumulator buffers of the segments that start in this stage
+                // (at most four, and the buffer of the fourth was released by a segment that ended in an
+                // earlier stage, so waiting for all of them up front cannot block on this stage's own
+                // MMAs); second pass: the MMAs and commits as one straight-line sequence
                 bool alive = true;
+                uint32_t dt[MMAS_PER_STAGE], kbuf[MMAS_PER_STAGE];
 #pragma unroll
                 for (int m = 0; m < MMAS_PER_STAGE; ++m) {
-                    if (m < nmma && alive) {
-                        const uint32_t f = kstep_flags(cmd, m);
-                        if (f & KS_FIRST) {                 // a new window segment: the next accumulator buffer
-                            buf = ai % NACC;
-                            const uint32_t aph = (ai / NACC) & 1u;
-                            ++ai;
-                            if (!mbar_wait_t<PROF>(smem_u32(&ss->acc_empty[buf]), aph ^ 1u, abort_flag, w_acc)) { raise(prm, ss, ST_TIMEOUT_ACC); alive = false; }
-                            tc_fence_after();
-                        }
-                        if (alive && !(prm.skip & 1)) {
-                            const uint32_t d_tmem = tmem_base + buf * C::kAccCols;
-#pragma unroll
-                            for (int h = 0; h < NH; ++h)
-                                umma_f16(d_tmem + h * 16, ad + (uint64_t)(((m * NH + h) * A_MMA_BYTES) >> 4),
-                                         bd + (uint64_t)((m * 2 * TILE_BYTES) >> 4), idesc, (f & KS_FIRST) ? 0u : 1u);
-                        }
-                        if (alive && (f & KS_LAST)) umma_commit(smem_u32(&ss->acc_full[buf]));
+                    if (m < nmma && alive && (kstep_flags(cmd, m) & KS_FIRST)) {
+                        buf = ai % NACC;
+                        const uint32_t aph = (ai / NACC) & 1u;
+                        ++ai;
+                        if (!mbar_wait_t<PROF>(smem_u32(&ss->acc_empty[buf]), aph ^ 1u, abort_flag, w_acc)) { raise(prm, ss, ST_TIMEOUT_ACC); alive = false; }
                     }
+                    kbuf[m] = buf;
+                    dt[m] = tmem_base + buf * C::kAccCols;
                 }
                 if (!alive) break;
+                tc_fence_after();
+#pragma unroll
+                for (int m = 0; m < MMAS_PER_STAGE; ++m) {
+                    if (m < nmma) {
+                        const uint32_t f = kstep_flags(cmd, m);
+                        if (!(prm.skip & 1)) {
+#pragma unroll
+                            for (int h = 0; h < NH; ++h)
+                                umma_f16(dt[m] + h * 16, ad + (uint64_t)(((m * NH + h) * A_MMA_BYTES) >> 4),
+                                         bd + (uint64_t)((m * 2 * TILE_BYTES) >> 4), idesc, (f & KS_FIRST) ? 0u : 1u);
+                        }
+                        if (f & KS_LAST) umma_commit(smem_u32(&ss->acc_full[kbuf[m]]));
+                    }
+                }
 #else
                 const int nmma = (int)((cmd & CMD_COUNT) + 1u) >> 1;
                 if (cmd & CMD_FIRST) {
