@@ -11,8 +11,14 @@ N(0,1).  One step = one forward product and one product with the cached transpos
 Prints ONE JSON line.  `value` is algorithmic GB/s (compulsory bytes of both products divided by
 device time, inputs resident in HBM); `e2e` is the same through the public `spmm_tc` /
 `spmm_transpose` calls with host buffers (pinned H2D of the dense operand and D2H of the result
-inside the timed region).  `--impl reference` times the CPU restatement of the reference path
-(oracle/, OpenMP over all host cores) on a bounded sample of the same workload.
+inside the timed region; the forward and the transposed chain run on two streams, so uploads and
+read-backs overlap).  `--impl reference` times the CPU restatement of the reference path
+(oracle/, OpenMP over all host cores) on the same workload.
+
+Secondary lines of the metric, same JSON contract: `--workload gcn_small` (GCN epoch ms on the
+2,708-node graph), `--workload gcn_full --scale S` (row-partitioned full-graph GCN epoch on the
+dense-community shape; strong scaling under torchrun), `--workload sampled --scale S` (sampled
+mini-batch training, seeds/s; weak scaling under torchrun).
 """
 import argparse
 import json
