@@ -50,6 +50,16 @@ def _device_visible(t: torch.Tensor, name: str):
         raise RuntimeError(f"{name} must be a CUDA tensor or pinned host memory")
 
 
+def check_device_status(device=None):
+    """Synchronises the current stream of ``device`` and raises RuntimeError (status -5) if any
+    tcgen05 SpMM launch on that device gave up on a pipeline wait since the last check: its output
+    is then incomplete.  The kernels' waits are bounded, so a broken pipeline ends with this status
+    instead of hanging the GPU.  Call it where the host synchronises anyway (end of an epoch)."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    with torch.cuda.device(device):
+        _native.check(_native.lib().grws_spmm_check(_stream(device)))
+
+
 def _scratch(nbytes: int, device):
     return torch.empty(max(int(nbytes), 16), dtype=torch.uint8, device=device)
 
@@ -57,7 +67,7 @@ def _scratch(nbytes: int, device):
 def spmm_raw(window_offset, cols, vals, B, out_dtype=None, algo=None, num_tiles_bound=None, check=False):
     """C[W*16, N] = A_bcsr @ B with values already in B's dtype and N % 8 == 0.
 
-    ``check=True`` synchronises and raises if the tcgen05 kernel reported a timed-out wait."""
+    ``check=True`` synchronises and raises if a tcgen05 launch reported a timed-out wait."""
     lib = _native.lib()
     W = window_offset.shape[0] - 1
     K, N = B.shape
@@ -73,10 +83,8 @@ def spmm_raw(window_offset, cols, vals, B, out_dtype=None, algo=None, num_tiles_
         _ptr(window_offset), _ptr(cols), _ptr(vals), _DT[vals.dtype], _ptr(B), _DT[B.dtype], B.stride(0),
         C.data_ptr(), _DT[out_dtype], N, W, T, K, N, scratch.data_ptr(), scratch.numel(), algo,
         _stream(B.device)))
-    if check and lib.grws_spmm_resolve_algo(_DT[vals.dtype], N, algo) == ALGO_TCGEN05:
-        status = int(scratch[:4].view(torch.int32).item())
-        if status != 0:
-            raise RuntimeError(f"grws_b200 error -5: tcgen05 SpMM pipeline wait timed out (code {status})")
+    if check:
+        check_device_status(B.device)
     return C
 
 
@@ -122,14 +130,16 @@ def spmm_tc(window_offset, original_col_indices, values_condensed, input_B, warp
 # CSR -> BCSR and the cached transposed BCSR
 # ---------------------------------------------------------------------------------------------
 def csr_to_bcsr(num_rows, row_ptr, col_idx, values, tile_rows=16, tile_cols=8, values_dtype=torch.float32,
-                exact=True):
+                exact=True, nnz_is_bound=False):
     """Device builder: CUDA tensors in, CUDA tensors out (window_offset, cols, vals).
 
     With ``exact`` the tile count is read back from the device to size ``cols`` / ``vals`` exactly
     (what the reference's builder returns).  ``exact=False`` skips that host synchronisation and
     sizes them by the bound ``entries / 8 + windows`` (every window wastes less than one tile): the
     arrays then end in unused tiles (column ids -1, values 0) which no kernel visits, since all of
-    them walk ``window_offset``.  Per-step builders (sampled blocks, their transposes) use it."""
+    them walk ``window_offset``.  Per-step builders (sampled blocks, their transposes) use it.
+    ``nnz_is_bound``: only the first ``row_ptr[num_rows]`` entries of ``col_idx`` / ``values`` exist,
+    their length is a bound (the caller did not read the count back either)."""
     if tile_rows != 16 or tile_cols != 8:
         raise RuntimeError("Currently only supports tile 16x8")
     lib = _native.lib()
@@ -142,8 +152,9 @@ def csr_to_bcsr(num_rows, row_ptr, col_idx, values, tile_rows=16, tile_cols=8, v
     wo = torch.empty(W + 1, dtype=torch.int64, device=dev)
     scratch = _scratch(lib.grws_csr_to_bcsr_scratch_bytes(num_rows, nnz), dev)
     st = _stream(dev)
-    _native.check(lib.grws_csr_to_bcsr_count(num_rows, _ptr(row_ptr), _ptr(col_idx), _ptr(values), nnz,
-                                             wo.data_ptr(), scratch.data_ptr(), scratch.numel(), st))
+    count = lib.grws_csr_to_bcsr_count_bounded if nnz_is_bound else lib.grws_csr_to_bcsr_count
+    _native.check(count(num_rows, _ptr(row_ptr), _ptr(col_idx), _ptr(values), nnz,
+                        wo.data_ptr(), scratch.data_ptr(), scratch.numel(), st))
     T = int(wo[-1].item()) if exact else nnz // 8 + W
     cols = torch.empty(T * 8, dtype=torch.int32, device=dev)
     vals = torch.empty(T * 128, dtype=values_dtype, device=dev)
@@ -163,9 +174,11 @@ def csr_to_bcsr_cpu(num_rows, row_ptr, col_idx, values, tile_rows, tile_cols):
     return wo.cpu(), cols.cpu(), vals.cpu()
 
 
-def bcsr_transpose(window_offset, cols, vals, num_cols, values_dtype=None, exact=True):
+def bcsr_transpose(window_offset, cols, vals, num_cols, values_dtype=None, exact=True, nnz_bound=None):
     """BCSR of A^T (rows = column ids of A, ``num_cols`` of them; columns = rows of A).
-    ``exact`` as in ``csr_to_bcsr``."""
+    ``exact`` as in ``csr_to_bcsr``.  ``nnz_bound``: an upper bound on the number of non-zero
+    entries that the caller knows without asking the device (a sampled block has at most
+    rows x fanout); with it the entry count is not read back either."""
     lib = _native.lib()
     dev = vals.device
     W = window_offset.shape[0] - 1
@@ -175,13 +188,14 @@ def bcsr_transpose(window_offset, cols, vals, num_cols, values_dtype=None, exact
     _native.check(lib.grws_bcsr_transpose_count(_ptr(window_offset), _ptr(cols), _ptr(vals), _DT[vals.dtype],
                                                 W, num_cols, row_ptr_t.data_ptr(), scratch.data_ptr(),
                                                 scratch.numel(), st))
-    nnz = int(row_ptr_t[-1].item())
+    nnz = int(row_ptr_t[-1].item()) if nnz_bound is None else int(nnz_bound)
     col_t = torch.empty(nnz, dtype=torch.int32, device=dev)
     val_t = torch.empty(nnz, dtype=torch.float32, device=dev)
     _native.check(lib.grws_bcsr_transpose_fill(_ptr(window_offset), _ptr(cols), _ptr(vals), _DT[vals.dtype],
                                                W, num_cols, row_ptr_t.data_ptr(), _ptr(col_t), _ptr(val_t),
                                                scratch.data_ptr(), scratch.numel(), st))
-    return csr_to_bcsr(num_cols, row_ptr_t, col_t, val_t, values_dtype=values_dtype or vals.dtype, exact=exact)
+    return csr_to_bcsr(num_cols, row_ptr_t, col_t, val_t, values_dtype=values_dtype or vals.dtype, exact=exact,
+                       nnz_is_bound=nnz_bound is not None)
 
 
 class _TransposeCache:
@@ -230,8 +244,10 @@ def spmm_transpose(window_offset, original_col_indices, values_condensed, grad_o
 
 
 from .sampling import (SamplingTimingResult, bcsr_to_csr, build_block, reindex_bcsr,  # noqa: E402,F401
-                       sample_all_layers, sample_hop, sample_layers_csr)
+                       sample_all_layers, sample_hop, sample_layers_csr, sample_layers_fused,
+                       sample_layers_sizes)
 
 __all__ = ["sample_all_layers", "spmm_tc", "spmm_transpose", "csr_to_bcsr_cpu", "reindex_bcsr",
            "csr_to_bcsr", "bcsr_transpose", "spmm_raw", "set_spmm_timing", "set_spmm_algo",
-           "bcsr_to_csr", "sample_hop", "build_block", "sample_layers_csr", "SamplingTimingResult"]
+           "check_device_status", "bcsr_to_csr", "sample_hop", "build_block", "sample_layers_csr", "sample_layers_fused",
+           "sample_layers_sizes", "SamplingTimingResult"]

@@ -26,9 +26,14 @@ SIGNATURES = {
                               c_i64, c_i64, c_i64, c_i64, c_vp, c_sz, c_i32, c_vp]),
     "grws_spmm_fwd_static": (c_i32, [c_vp, c_vp, c_vp, c_i32, c_vp, c_i32, c_i64, c_vp, c_i32, c_i64,
                                      c_i64, c_i64, c_i64, c_i64, c_vp]),
+    "grws_spmm_last_status": (c_i32, [c_vp, c_i32, c_vp]),
+    "grws_spmm_check": (c_i32, [c_vp]),
+    "grws_spmm_set_wait_limit": (c_i32, [ctypes.c_longlong]),
     "grws_csr_to_bcsr_scratch_bytes": (c_sz, [c_i64, c_i64]),
     "grws_csr_to_bcsr_count": (c_i32, [c_i64, c_vp, c_vp, c_vp, c_i64, c_vp, c_vp, c_sz, c_vp]),
     "grws_csr_to_bcsr_fill": (c_i32, [c_i64, c_i64, c_vp, c_i64, c_vp, c_vp, c_i32, c_vp, c_sz, c_vp]),
+    "grws_csr_to_bcsr_count_bounded": (c_i32, [c_i64, c_vp, c_vp, c_vp, c_i64, c_vp, c_vp, c_sz, c_vp]),
+    "grws_block_build_count": (c_i32, [c_vp, c_vp, c_i64, c_i32, c_vp, c_vp, c_sz, c_vp]),
     "grws_bcsr_transpose_scratch_bytes": (c_sz, [c_i64]),
     "grws_bcsr_transpose_count": (c_i32, [c_vp, c_vp, c_vp, c_i32, c_i64, c_i64, c_vp, c_vp, c_sz, c_vp]),
     "grws_bcsr_transpose_fill": (c_i32, [c_vp, c_vp, c_vp, c_i32, c_i64, c_i64, c_vp, c_vp, c_vp,
@@ -41,6 +46,10 @@ SIGNATURES = {
     "grws_dedup_scratch_bytes": (c_sz, [c_i64, c_i32]),
     "grws_dedup_reindex": (c_i32, [c_vp, c_i64, c_vp, c_i32, c_vp, c_vp, c_vp, c_vp, c_vp, c_sz, c_vp]),
     "grws_block_compact": (c_i32, [c_vp, c_vp, c_i64, c_i32, c_vp, c_vp, c_vp, c_vp]),
+    "grws_sample_layers_sizes": (c_i32, [c_i64, c_vp, c_i32, c_i64, c_vp, c_vp, c_vp]),
+    "grws_sample_layers_scratch_bytes": (c_sz, [c_i64, c_vp, c_i32, c_i64]),
+    "grws_sample_layers": (c_i32, [c_vp, c_vp, c_vp, c_vp, c_i64, c_vp, c_i32, ctypes.c_uint64, c_vp, c_i64, c_i32,
+                                   c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_sz, c_vp]),
     "grws_reindex_bcsr": (c_i32, [c_vp, c_vp, c_i32, c_vp, c_i64, c_i64, c_i32, c_i32, c_vp, c_vp]),
 }
 

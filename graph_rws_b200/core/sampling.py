@@ -135,6 +135,68 @@ def sample_layers_csr(row_ptr, col_idx, values, seeds, fanouts, seed=DEFAULT_SEE
     return out, timings
 
 
+def sample_layers_sizes(num_seeds, fanouts, pad_to=0):
+    """(n_dst, n_src, tiles_bound) per hop of ``sample_layers_fused``: the sizes every buffer of a
+    mini-batch gets, known from the seed count and the fanouts alone."""
+    import ctypes
+    lib = _native.lib()
+    L = len(fanouts)
+    fan = (ctypes.c_int * L)(*[int(f) for f in fanouts])
+    a, b, c = ((ctypes.c_int64 * L)() for _ in range(3))
+    _native.check(lib.grws_sample_layers_sizes(int(num_seeds), fan, L, int(pad_to), a, b, c))
+    return list(a), list(b), list(c)
+
+
+def sample_layers_fused(row_ptr, col_idx, values, seeds, fanouts, seed=DEFAULT_SEED, values_dtype=torch.float32,
+                        pad_to=0, seed_dev=None, want_counts=False):
+    """All hops of a mini-batch in ONE library call and without any size read-back.
+
+    Same sampling, dedup and block layout as ``sample_layers_csr``; what differs is the sizing: every
+    hop's arrays have the bound sizes of ``sample_layers_sizes`` (the frontier of hop h+1 is the
+    whole source list of hop h, its unused tail filled with -1 nodes that sample nothing), so the
+    shapes of a step depend only on (number of seeds, fanouts) and recur from step to step.  The
+    call queues about twenty kernels per hop on the current stream and returns; ctypes releases the
+    interpreter lock for its duration, so a sampling thread does not hold up the training thread.
+
+    Returns one [window_offset, cols, vals, dst_nodes, src_nodes] list per hop (fanouts in the order
+    given) and, with ``want_counts``, an int64 [hops, 4] device tensor {source nodes, sampled edges,
+    tiles, real frontier nodes} per hop."""
+    import ctypes
+    lib = _native.lib()
+    dev = row_ptr.device
+    seeds = seeds.to(device=dev, dtype=torch.int32).contiguous()
+    L = len(fanouts)
+    n_dst, n_src, tiles = sample_layers_sizes(seeds.numel(), fanouts, pad_to)
+    fan = (ctypes.c_int * L)(*[int(f) for f in fanouts])
+    vsize = torch.empty((), dtype=values_dtype).element_size()
+    # one allocation for all int32 outputs, one for the values, one for the offsets, one for scratch
+    i32_sizes = [n for h in range(L) for n in (n_src[h], tiles[h] * 8)]
+    i32 = torch.empty(sum(-(-n // 64) * 64 for n in i32_sizes) + 64, dtype=torch.int32, device=dev)
+    vals_all = torch.empty(sum(t * 128 for t in tiles) + 8, dtype=values_dtype, device=dev)
+    wo_sizes = [(n + 15) // 16 + 1 for n in n_dst]
+    wo_all = torch.empty(sum(-(-n // 32) * 32 for n in wo_sizes) + 4 * L, dtype=torch.int64, device=dev)
+    scratch = _scratch(lib.grws_sample_layers_scratch_bytes(seeds.numel(), fan, L, int(pad_to)), dev)
+    srcs, cols, vals, wos = [], [], [], []
+    o32 = ov = ow = 0
+    for h in range(L):
+        srcs.append(i32[o32:o32 + n_src[h]]); o32 += -(-n_src[h] // 64) * 64
+        cols.append(i32[o32:o32 + tiles[h] * 8]); o32 += -(-(tiles[h] * 8) // 64) * 64
+        vals.append(vals_all[ov:ov + tiles[h] * 128]); ov += tiles[h] * 128
+        wos.append(wo_all[ow:ow + wo_sizes[h]]); ow += -(-wo_sizes[h] // 32) * 32
+    counts = wo_all[ow:ow + 4 * L].view(L, 4) if want_counts else None
+    ptrs = lambda ts: (ctypes.c_void_p * L)(*[t.data_ptr() for t in ts])      # noqa: E731
+    _native.check(lib.grws_sample_layers(
+        _ptr(row_ptr), _ptr(col_idx), _ptr(values), _ptr(seeds), seeds.numel(), fan, L,
+        int(seed) & 0xFFFFFFFFFFFFFFFF, _ptr(seed_dev), int(pad_to), _DT[values_dtype],
+        ptrs(srcs), ptrs(wos), ptrs(cols), ptrs(vals), _ptr(counts) if want_counts else 0,
+        scratch.data_ptr(), scratch.numel(), _stream(dev)))
+    out, dst = [], seeds
+    for h in range(L):
+        out.append([wos[h], cols[h], vals[h], dst, srcs[h]])
+        dst = srcs[h]
+    return (out, counts) if want_counts else out
+
+
 class _CsrCache:
     """CSR views of the BCSR graphs recently passed to ``sample_all_layers`` (keyed on tensor
     identity and version; entries keep the tensors alive so storage cannot be recycled)."""

@@ -19,6 +19,7 @@ int spmm_tc5_launch(const int64_t *, const int32_t *, const void *, int, const v
                     void *, int, int64_t, int64_t, int64_t, int64_t, int64_t, void *, size_t,
                     cudaStream_t);
 size_t spmm_tc5_scratch_bytes(int64_t num_tiles_bound, int64_t N);
+int spmm_zero_output(void *C, int c_dtype, int64_t ldc, int64_t W, int64_t N, cudaStream_t stream);
 
 }  // namespace grws
 
@@ -68,6 +69,8 @@ int grws_spmm_fwd(const int64_t *window_offset, const int32_t *cols, const void 
     GRWS_REQUIRE(aligned16(B) && aligned16(C) && aligned16(vals) && aligned16(cols) && aligned16(scratch),
                  "B, C, values, column ids and scratch must be 16-byte aligned");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    // no tiles, or no dense rows (every column id is then out of range): the product is zero rows
+    if (num_tiles_bound == 0 || K == 0) return spmm_zero_output(C, c_dtype, ldc, num_windows, N, st);
     bool tc5 = false;
     if (algo == GRWS_SPMM_TCGEN05) {
         if (!spmm_tc5_supported(val_dtype, N))

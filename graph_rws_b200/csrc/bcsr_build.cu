@@ -20,6 +20,10 @@
 namespace grws {
 
 constexpr int ROW_BITS = 4;   // row inside a 16-row window
+// Key of an entry that does not exist (a padding slot of a fixed-stride neighbour list, the unused
+// tail of a CSR array sized by a bound).  Real keys are below it (fewer than 2^28 windows), so such
+// entries sort to the end; they open no column slot and write nothing.
+constexpr uint64_t INVALID_KEY = ~0ull;
 
 static inline size_t align_up(size_t x, size_t a = 256) { return (x + a - 1) / a * a; }
 
@@ -81,10 +85,23 @@ __global__ void make_keys_kernel(int64_t num_rows, const int64_t *__restrict__ r
         keys[e] = hi | ((uint64_t)(uint32_t)col_idx[e] << ROW_BITS) | lo;
 }
 
+// keys of a hop's fixed-stride neighbour lists: entry (row i, slot j) holds local column id
+// local[i * fanout + j], or -1 when the slot is empty
+__global__ void make_keys_lists_kernel(int64_t n_entries, int fanout, const int32_t *__restrict__ local,
+                                       uint64_t *__restrict__ keys) {
+    const int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= n_entries) return;
+    const int32_t c = local[e];
+    const int64_t row = e / fanout;
+    keys[e] = c < 0 ? INVALID_KEY
+                    : (((uint64_t)(row / TILE_ROWS) << (32 + ROW_BITS)) | ((uint64_t)(uint32_t)c << ROW_BITS) | (uint64_t)(row % TILE_ROWS));
+}
+
 __global__ void head_flags_kernel(int64_t nnz, const uint64_t *__restrict__ keys,
                                   int32_t *__restrict__ flags, int32_t *__restrict__ nuniq) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= nnz) return;
+    if (keys[i] == INVALID_KEY) { flags[i] = 0; return; }
     const uint64_t k = keys[i] >> ROW_BITS;
     const bool head = (i == 0) || ((keys[i - 1] >> ROW_BITS) != k);
     flags[i] = head ? 1 : 0;
@@ -110,6 +127,7 @@ __global__ void fill_kernel(int64_t nnz, const uint64_t *__restrict__ keys, cons
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= nnz) return;
     const uint64_t key = keys[i];
+    if (key == INVALID_KEY) return;
     if (i + 1 < nnz && keys[i + 1] == key) return;          // an identical (row, column) follows: it wins
     const int64_t w = (int64_t)(key >> (32 + ROW_BITS));
     const int32_t col = (int32_t)((key >> ROW_BITS) & 0xffffffffu);
@@ -197,6 +215,34 @@ __global__ void bcsr_rows_kernel(int64_t W, int64_t num_rows, const int64_t *__r
 
 using namespace grws;
 
+// Second half of the count phase, shared by the CSR and the neighbour-list front ends: sorts the
+// keys in s.keys_a (values alongside), flags the first entry of every (window, column) run and
+// turns the unique-column counts into window_offset.
+static int count_from_keys(const BuildScratch &s, int64_t nnz, int64_t W, const float *values,
+                           int64_t *window_offset, cudaStream_t st) {
+    GRWS_CUDA_TRY(cudaMemsetAsync(s.nuniq, 0, (size_t)(W + 2) * 4, st));
+    if (nnz > 0) {
+        size_t tmp = s.cub_bytes;
+        // only the bits a key can use are sorted; the invalid key is all ones there too, so it
+        // still sorts behind every real key (no column id is 0xffffffff)
+        int end_bit = 32 + ROW_BITS;
+        for (int64_t x = W; x > 0; x >>= 1) ++end_bit;
+        if (end_bit > 64) end_bit = 64;
+        GRWS_CUDA_TRY(cub::DeviceRadixSort::SortPairs(s.cub_tmp, tmp, s.keys_a, s.keys_b, values, s.vals_b,
+                                                      (int)nnz, 0, end_bit, st));
+        head_flags_kernel<<<blocks_for(nnz, 256), 256, 0, st>>>(nnz, s.keys_b, s.flags, s.nuniq);
+        tmp = s.cub_bytes;
+        GRWS_CUDA_TRY(cub::DeviceScan::InclusiveSum(s.cub_tmp, tmp, s.flags, s.uidx, (int)nnz, st));
+    }
+    tiles_kernel<<<blocks_for(W + 1, 256), 256, 0, st>>>(W, s.nuniq, s.tiles);
+    size_t tmp = s.cub_bytes;
+    GRWS_CUDA_TRY(cub::DeviceScan::InclusiveSum(s.cub_tmp, tmp, s.tiles, window_offset, (int)(W + 1), st));
+    tmp = s.cub_bytes;
+    GRWS_CUDA_TRY(cub::DeviceScan::ExclusiveSum(s.cub_tmp, tmp, s.nuniq, s.ufirst, (int)(W + 1), st));
+    GRWS_CUDA_TRY(cudaGetLastError());
+    return GRWS_OK;
+}
+
 template <typename T>
 static int transpose_count(const int64_t *wo, const int32_t *cols, const void *vals, int64_t W, int64_t num_cols,
                            int64_t *row_ptr_t, void *scratch, cudaStream_t st) {
@@ -221,10 +267,9 @@ size_t grws_csr_to_bcsr_scratch_bytes(int64_t num_rows, int64_t nnz) {
     return carve(nullptr, nnz, ceil_div(num_rows, TILE_ROWS)).total;
 }
 
-__attribute__((visibility("default")))
-int grws_csr_to_bcsr_count(int64_t num_rows, const int64_t *row_ptr, const int32_t *col_idx,
-                           const float *values, int64_t nnz, int64_t *window_offset, void *scratch,
-                           size_t scratch_bytes, void *stream) {
+static int csr_count(int64_t num_rows, const int64_t *row_ptr, const int32_t *col_idx, const float *values,
+                     int64_t nnz, bool nnz_is_bound, int64_t *window_offset, void *scratch, size_t scratch_bytes,
+                     void *stream) {
     GRWS_REQUIRE(num_rows >= 0 && nnz >= 0, "negative size");
     GRWS_REQUIRE(nnz < 0x7fffffffLL, "csr_to_bcsr handles fewer than 2^31 entries");
     const int64_t W = ceil_div(num_rows, TILE_ROWS);
@@ -234,26 +279,42 @@ int grws_csr_to_bcsr_count(int64_t num_rows, const int64_t *row_ptr, const int32
     BuildScratch s = carve(scratch, nnz, W);
     if (scratch_bytes < s.total) return fail(GRWS_ERR_SCRATCH, "csr_to_bcsr scratch too small: %zu < %zu", scratch_bytes, s.total);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    GRWS_CUDA_TRY(cudaMemsetAsync(s.nuniq, 0, (size_t)(W + 2) * 4, st));
     if (nnz > 0) {
+        // entries of the arrays past row_ptr[num_rows] (a CSR sized by a bound) keep the invalid key
+        if (nnz_is_bound) GRWS_CUDA_TRY(cudaMemsetAsync(s.keys_a, 0xff, (size_t)nnz * 8, st));
         make_keys_kernel<<<blocks_for(num_rows * 32, 256), 256, 0, st>>>(num_rows, row_ptr, col_idx, s.keys_a);
-        size_t tmp = s.cub_bytes;
-        int end_bit = 32 + ROW_BITS;
-        for (int64_t x = W; x > 0; x >>= 1) ++end_bit;
-        if (end_bit > 64) end_bit = 64;
-        GRWS_CUDA_TRY(cub::DeviceRadixSort::SortPairs(s.cub_tmp, tmp, s.keys_a, s.keys_b, values, s.vals_b,
-                                                      (int)nnz, 0, end_bit, st));
-        head_flags_kernel<<<blocks_for(nnz, 256), 256, 0, st>>>(nnz, s.keys_b, s.flags, s.nuniq);
-        tmp = s.cub_bytes;
-        GRWS_CUDA_TRY(cub::DeviceScan::InclusiveSum(s.cub_tmp, tmp, s.flags, s.uidx, (int)nnz, st));
     }
-    tiles_kernel<<<blocks_for(W + 1, 256), 256, 0, st>>>(W, s.nuniq, s.tiles);
-    size_t tmp = s.cub_bytes;
-    GRWS_CUDA_TRY(cub::DeviceScan::InclusiveSum(s.cub_tmp, tmp, s.tiles, window_offset, (int)(W + 1), st));
-    tmp = s.cub_bytes;
-    GRWS_CUDA_TRY(cub::DeviceScan::ExclusiveSum(s.cub_tmp, tmp, s.nuniq, s.ufirst, (int)(W + 1), st));
-    GRWS_CUDA_TRY(cudaGetLastError());
-    return GRWS_OK;
+    return count_from_keys(s, nnz, W, values, window_offset, st);
+}
+
+__attribute__((visibility("default")))
+int grws_csr_to_bcsr_count(int64_t num_rows, const int64_t *row_ptr, const int32_t *col_idx,
+                           const float *values, int64_t nnz, int64_t *window_offset, void *scratch,
+                           size_t scratch_bytes, void *stream) {
+    return csr_count(num_rows, row_ptr, col_idx, values, nnz, false, window_offset, scratch, scratch_bytes, stream);
+}
+
+__attribute__((visibility("default")))
+int grws_csr_to_bcsr_count_bounded(int64_t num_rows, const int64_t *row_ptr, const int32_t *col_idx,
+                                   const float *values, int64_t nnz_bound, int64_t *window_offset, void *scratch,
+                                   size_t scratch_bytes, void *stream) {
+    return csr_count(num_rows, row_ptr, col_idx, values, nnz_bound, true, window_offset, scratch, scratch_bytes, stream);
+}
+
+__attribute__((visibility("default")))
+int grws_block_build_count(const int32_t *local, const float *w, int64_t n_dst, int fanout, int64_t *window_offset,
+                           void *scratch, size_t scratch_bytes, void *stream) {
+    GRWS_REQUIRE(n_dst >= 0 && fanout > 0, "bad size");
+    const int64_t n_entries = n_dst * fanout;
+    GRWS_REQUIRE(n_entries < 0x7fffffffLL, "hop too large");
+    const int64_t W = ceil_div(n_dst, TILE_ROWS);
+    GRWS_REQUIRE(window_offset && scratch && (n_entries == 0 || (local && w)), "null pointer");
+    BuildScratch s = carve(scratch, n_entries, W);
+    if (scratch_bytes < s.total) return fail(GRWS_ERR_SCRATCH, "block build scratch too small: %zu < %zu", scratch_bytes, s.total);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (n_entries > 0)
+        make_keys_lists_kernel<<<blocks_for(n_entries, 256), 256, 0, st>>>(n_entries, fanout, local, s.keys_a);
+    return count_from_keys(s, n_entries, W, w, window_offset, st);
 }
 
 __attribute__((visibility("default")))

@@ -59,9 +59,10 @@ __device__ __forceinline__ uint64_t sample_draw64(uint64_t seed, uint32_t node, 
 __global__ void __launch_bounds__(SAMPLE_WARPS * 32)
 sample_hop_kernel(const int64_t *__restrict__ row_ptr, const int32_t *__restrict__ col_idx,
                   const float *__restrict__ values, const int32_t *__restrict__ nodes, int64_t n,
-                  int fanout, uint64_t seed, uint32_t hop, int32_t *__restrict__ out_nbr,
-                  float *__restrict__ out_w, int32_t *__restrict__ out_cnt) {
+                  int fanout, uint64_t seed, const uint64_t *__restrict__ seed_dev, uint32_t hop,
+                  int32_t *__restrict__ out_nbr, float *__restrict__ out_w, int32_t *__restrict__ out_cnt) {
     __shared__ int64_t picks[SAMPLE_WARPS][MAX_FANOUT];
+    if (seed_dev) seed = *seed_dev;          // a seed that changes between replays of one captured launch
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t i = (int64_t)blockIdx.x * SAMPLE_WARPS + warp;
     if (i >= n) return;
@@ -236,6 +237,47 @@ __global__ void reindex_kernel(const int32_t *__restrict__ in_cols, T *__restric
     }
 }
 
+// one launch instead of four fills: empty hash table, candidate list of sentinels, zero counter,
+// and the part of the source list behind the destination nodes set to -1
+__global__ void dedup_init_kernel(int32_t *keys, int32_t *vals, int64_t slots, int32_t *cand, int64_t n_cand,
+                                  int32_t *n_new, int32_t *src_tail, int64_t n_tail) {
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x, i0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    for (int64_t i = i0; i < slots; i += stride) { keys[i] = EMPTY_KEY; vals[i] = NEW_NODE; }
+    for (int64_t i = i0; i < n_cand; i += stride) cand[i] = NEW_NODE;
+    for (int64_t i = i0; i < n_tail; i += stride) src_tail[i] = -1;
+    if (i0 == 0) *n_new = 0;
+}
+
+// local id of every sampled neighbour (one thread per list slot)
+__global__ void localize_flat_kernel(const int32_t *__restrict__ nbr, int64_t n_entries, const int32_t *keys,
+                                     const int32_t *vals, uint32_t mask, int32_t *__restrict__ out_local) {
+    const int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= n_entries) return;
+    const int32_t u = nbr[e];
+    out_local[e] = u >= 0 ? table_lookup(keys, vals, mask, u) : -1;
+}
+
+// per-hop figures for the caller: {source nodes (padded destinations + new nodes), sampled edges,
+// tiles of the block, real (non-padding) frontier nodes}
+__global__ void hop_counts_kernel(const int32_t *__restrict__ n_new, const int32_t *__restrict__ dst, int64_t n_dst,
+                                  const int32_t *__restrict__ cnt, const int64_t *__restrict__ window_offset, int64_t W,
+                                  int64_t *__restrict__ out) {
+    __shared__ unsigned long long s_edges, s_real;
+    if (threadIdx.x == 0) { s_edges = 0; s_real = 0; }
+    __syncthreads();
+    unsigned long long e = 0, r = 0;
+    for (int64_t i = threadIdx.x; i < n_dst; i += blockDim.x) { e += (unsigned long long)cnt[i]; r += dst[i] >= 0 ? 1 : 0; }
+    atomicAdd(&s_edges, e);
+    atomicAdd(&s_real, r);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        out[0] = n_dst + *n_new;
+        out[1] = (int64_t)s_edges;
+        out[2] = window_offset[W];
+        out[3] = (int64_t)s_real;
+    }
+}
+
 static inline size_t up256(size_t x) { return (x + 255) / 256 * 256; }
 static inline unsigned nblocks(int64_t n, int t) { int64_t b = (n + t - 1) / t; return (unsigned)(b < 1 ? 1 : b); }
 
@@ -284,7 +326,7 @@ int grws_sample_hop(const int64_t *row_ptr, const int32_t *col_idx, const float 
     if (num_nodes == 0) return GRWS_OK;
     GRWS_REQUIRE(row_ptr && col_idx && nodes && out_nbr && out_w, "null pointer");
     sample_hop_kernel<<<nblocks(num_nodes, SAMPLE_WARPS), SAMPLE_WARPS * 32, 0, static_cast<cudaStream_t>(stream)>>>(
-        row_ptr, col_idx, values, nodes, num_nodes, fanout, seed, hop, out_nbr, out_w, out_cnt);
+        row_ptr, col_idx, values, nodes, num_nodes, fanout, seed, nullptr, hop, out_nbr, out_w, out_cnt);
     GRWS_CUDA_TRY(cudaGetLastError());
     return GRWS_OK;
 }
@@ -359,6 +401,131 @@ int grws_reindex_bcsr(const int32_t *in_cols, void *values, int val_dtype, const
     else
         return fail(GRWS_ERR_UNSUPPORTED, "bad value dtype %d", val_dtype);
     GRWS_CUDA_TRY(cudaGetLastError());
+    return GRWS_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// All hops of one mini-batch in one call: sample, dedup / reindex, block build, per hop, with
+// every buffer sized by a bound that the host knows from (num_seeds, fanouts) alone, so nothing
+// is read back between the hops.
+// ---------------------------------------------------------------------------------------------
+__attribute__((visibility("default")))
+int grws_sample_layers_sizes(int64_t num_seeds, const int *fanouts, int num_hops, int64_t pad_to,
+                             int64_t *n_dst, int64_t *n_src, int64_t *tiles_bound) {
+    GRWS_REQUIRE(num_seeds >= 0 && num_hops >= 1 && num_hops <= 16 && fanouts && pad_to >= 0, "bad argument");
+    int64_t d = num_seeds;
+    for (int h = 0; h < num_hops; ++h) {
+        GRWS_REQUIRE(fanouts[h] > 0 && fanouts[h] <= MAX_FANOUT, "fanout %d outside [1, %d]", fanouts[h], MAX_FANOUT);
+        int64_t s = d * (1 + (int64_t)fanouts[h]);
+        if (pad_to > 1) s = ceil_div(s, pad_to) * pad_to;
+        GRWS_REQUIRE(s < 0x7fffffffLL, "hop %d too large", h);
+        if (n_dst) n_dst[h] = d;
+        if (n_src) n_src[h] = s;
+        if (tiles_bound) tiles_bound[h] = d * fanouts[h] / TILE_COLS + ceil_div(d, TILE_ROWS);
+        d = s;
+    }
+    return GRWS_OK;
+}
+
+// builder scratch, defined in bcsr_build.cu
+size_t grws_csr_to_bcsr_scratch_bytes(int64_t num_rows, int64_t nnz);
+int grws_block_build_count(const int32_t *local, const float *w, int64_t n_dst, int fanout, int64_t *window_offset,
+                           void *scratch, size_t scratch_bytes, void *stream);
+int grws_csr_to_bcsr_fill(int64_t num_rows, int64_t nnz, const int64_t *window_offset, int64_t num_tiles,
+                          int32_t *out_cols, void *out_vals, int val_dtype, void *scratch, size_t scratch_bytes,
+                          void *stream);
+
+struct LayersScratch {
+    int32_t *nbr, *local, *cnt;
+    float *w;
+    void *dedup, *build;
+    size_t dedup_bytes, build_bytes, total;
+};
+
+static int carve_layers(void *base, int64_t num_seeds, const int *fanouts, int num_hops, int64_t pad_to, LayersScratch *out) {
+    int64_t n_dst[16], n_src[16];
+    if (int st = grws_sample_layers_sizes(num_seeds, fanouts, num_hops, pad_to, n_dst, n_src, nullptr)) return st;
+    size_t entries = 1, rows = 1, dedup = 0, build = 0;
+    for (int h = 0; h < num_hops; ++h) {
+        const size_t e = (size_t)n_dst[h] * fanouts[h];
+        if (e > entries) entries = e;
+        if ((size_t)n_dst[h] > rows) rows = (size_t)n_dst[h];
+        const size_t d = carve_dedup(nullptr, n_dst[h], fanouts[h]).total, b = grws_csr_to_bcsr_scratch_bytes(n_dst[h], (int64_t)e);
+        if (d > dedup) dedup = d;
+        if (b > build) build = b;
+    }
+    char *p = static_cast<char *>(base);
+    size_t off = 0;
+    auto take = [&](size_t bytes) { char *q = p ? p + off : nullptr; off += up256(bytes); return (void *)q; };
+    out->nbr = (int32_t *)take(entries * 4);
+    out->w = (float *)take(entries * 4);
+    out->local = (int32_t *)take(entries * 4);
+    out->cnt = (int32_t *)take(rows * 4);
+    out->dedup = take(dedup);
+    out->build = take(build);
+    out->dedup_bytes = dedup;
+    out->build_bytes = build;
+    out->total = off;
+    return GRWS_OK;
+}
+
+__attribute__((visibility("default")))
+size_t grws_sample_layers_scratch_bytes(int64_t num_seeds, const int *fanouts, int num_hops, int64_t pad_to) {
+    LayersScratch s;
+    if (carve_layers(nullptr, num_seeds, fanouts, num_hops, pad_to, &s) != GRWS_OK) return 0;
+    return s.total;
+}
+
+__attribute__((visibility("default")))
+int grws_sample_layers(const int64_t *row_ptr, const int32_t *col_idx, const float *values, const int32_t *seeds,
+                       int64_t num_seeds, const int *fanouts, int num_hops, uint64_t seed, const uint64_t *seed_dev,
+                       int64_t pad_to, int val_dtype, int32_t *const *out_src, int64_t *const *out_window_offset,
+                       int32_t *const *out_cols, void *const *out_vals, int64_t *out_counts, void *scratch,
+                       size_t scratch_bytes, void *stream) {
+    GRWS_REQUIRE(row_ptr && col_idx && (seeds || num_seeds == 0) && out_src && out_window_offset && out_cols && out_vals && scratch,
+                 "null pointer");
+    GRWS_REQUIRE(val_dtype >= GRWS_F32 && val_dtype <= GRWS_BF16, "bad value dtype %d", val_dtype);
+    int64_t n_dst[16], n_src[16], tiles[16];
+    if (int st = grws_sample_layers_sizes(num_seeds, fanouts, num_hops, pad_to, n_dst, n_src, tiles)) return st;
+    LayersScratch s;
+    if (int st = carve_layers(scratch, num_seeds, fanouts, num_hops, pad_to, &s)) return st;
+    if (scratch_bytes < s.total) return fail(GRWS_ERR_SCRATCH, "sample_layers scratch too small: %zu < %zu", scratch_bytes, s.total);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int32_t *dst = seeds;
+    for (int h = 0; h < num_hops; ++h) {
+        const int64_t nd = n_dst[h], f = fanouts[h], n_entries = nd * f, W = ceil_div(nd, (int64_t)TILE_ROWS);
+        GRWS_REQUIRE(out_src[h] && out_window_offset[h] && (tiles[h] == 0 || (out_cols[h] && out_vals[h])), "null output of hop %d", h);
+        if (nd == 0) {
+            GRWS_CUDA_TRY(cudaMemsetAsync(out_window_offset[h], 0, 8, st));
+            if (n_src[h] > 0) GRWS_CUDA_TRY(cudaMemsetAsync(out_src[h], 0xff, (size_t)n_src[h] * 4, st));
+            if (out_counts) GRWS_CUDA_TRY(cudaMemsetAsync(out_counts + 4 * h, 0, 32, st));
+            dst = out_src[h];
+            continue;
+        }
+        // 1. neighbours of every frontier node (padding entries of the frontier, -1, get empty lists)
+        sample_hop_kernel<<<nblocks(nd, SAMPLE_WARPS), SAMPLE_WARPS * 32, 0, st>>>(
+            row_ptr, col_idx, values, dst, nd, (int)f, seed, seed_dev, (uint32_t)h, s.nbr, s.w, s.cnt);
+        // 2. source list = frontier ++ ascending new nodes ++ -1 padding; local id of every neighbour
+        DedupScratch d = carve_dedup(s.dedup, nd, (int)f);
+        const uint32_t mask = d.slots - 1;
+        const int64_t init_n = (int64_t)d.slots > n_src[h] ? (int64_t)d.slots : n_src[h];
+        dedup_init_kernel<<<nblocks(init_n, 256) > 1184 ? 1184 : nblocks(init_n, 256), 256, 0, st>>>(
+            d.keys, d.vals, d.slots, d.cand, n_entries + 1, d.n_new, out_src[h] + nd, n_src[h] - nd);
+        insert_dst_kernel<<<nblocks(nd, 256), 256, 0, st>>>(dst, nd, d.keys, d.vals, mask, out_src[h]);
+        insert_nbr_kernel<<<nblocks(n_entries, 256), 256, 0, st>>>(s.nbr, n_entries, d.keys, d.vals, mask, d.cand, d.n_new);
+        size_t tmp = d.cub_bytes;
+        GRWS_CUDA_TRY(cub::DeviceRadixSort::SortKeys(d.cub_tmp, tmp, d.cand, d.cand_sorted, (int)n_entries, 0, 32, st));
+        rank_new_kernel<<<nblocks(n_entries, 256), 256, 0, st>>>(d.cand_sorted, d.n_new, nd, d.keys, d.vals, mask, out_src[h]);
+        localize_flat_kernel<<<nblocks(n_entries, 256), 256, 0, st>>>(s.nbr, n_entries, d.keys, d.vals, mask, s.local);
+        // 3. the hop's BCSR block straight from the fixed-stride lists
+        if (int e = grws_block_build_count(s.local, s.w, nd, (int)f, out_window_offset[h], s.build, s.build_bytes, stream)) return e;
+        if (int e = grws_csr_to_bcsr_fill(nd, n_entries, out_window_offset[h], tiles[h], out_cols[h], out_vals[h], val_dtype,
+                                          s.build, s.build_bytes, stream)) return e;
+        if (out_counts)
+            hop_counts_kernel<<<1, 1024, 0, st>>>(d.n_new, dst, nd, s.cnt, out_window_offset[h], W, out_counts + 4 * h);
+        GRWS_CUDA_TRY(cudaGetLastError());
+        dst = out_src[h];
+    }
     return GRWS_OK;
 }
 

@@ -59,53 +59,33 @@ constexpr int A_MMA_BYTES = 4 * A_ATOM_BYTES;        // one K-step of one slab
 constexpr int TILE_BYTES = TILE_ELEMS * 2;           // 256
 constexpr int META_TILE_BYTES = STAGE_TILES * TILE_BYTES;
 constexpr int META_COL_BYTES = STAGE_TILES * TILE_COLS * 4;
-constexpr int META_CMD_BYTES = 16;                   // per-stage command word written by the TMA warp
+constexpr int META_CMD_BYTES = 16;                   // per-stage command word, copied from the stage's descriptor
 constexpr int META_BYTES = META_TILE_BYTES + META_COL_BYTES + META_CMD_BYTES;
 // command word: bits 0-4 tile count, bit 8 first stage of a window segment, bit 9 last stage,
 // bit 10 end of this CTA's work
-#ifndef GRWS_TC5_SPAN
-#define GRWS_TC5_SPAN 0
-#endif
-#if GRWS_TC5_SPAN
-// Stages that span windows: a stage is MMAS_PER_STAGE K-steps (tile pairs), each of which belongs
-// to one window segment.  Command word: bits 0-2 number of K-steps, bits 4+3i .. 6+3i the flags of
-// K-step i (first of its segment, last of its segment, second tile absent), bit 31 end of work.
-constexpr uint32_t CMD_COUNT = 7u, CMD_END = 1u << 31;
-constexpr uint32_t KS_FIRST = 1u, KS_LAST = 2u, KS_SINGLE = 4u;
-__device__ __forceinline__ uint32_t kstep_flags(uint32_t cmd, int i) { return (cmd >> (4 + 3 * i)) & 7u; }
-constexpr uint32_t CMD_FIRST = 0, CMD_LAST = 0;      // unused in this mode
-#else
 constexpr uint32_t CMD_COUNT = 31u, CMD_FIRST = 1u << 8, CMD_LAST = 1u << 9, CMD_END = 1u << 10;
-#endif
-static_assert((GRWS_TC5_SPAN ? MMAS_PER_STAGE : STAGE_TILES) <= (int)CMD_COUNT && STAGE_TILES % 2 == 0, "count field of the command word");
-static_assert(!GRWS_TC5_SPAN || MMAS_PER_STAGE <= 9, "K-step flags of the command word");
+static_assert(STAGE_TILES <= (int)CMD_COUNT && STAGE_TILES % 4 == 0, "count field of the command word; K-steps are issued in pairs");
 #ifndef GRWS_TC5_NACC
 #define GRWS_TC5_NACC 4
 #endif
-constexpr int NACC = GRWS_TC5_NACC;                              // accumulator buffers in tensor memory
-#ifndef GRWS_TC5_PRODUCER_WARPS
-#define GRWS_TC5_PRODUCER_WARPS 5
-#endif
-constexpr int NUM_PRODUCER_WARPS = GRWS_TC5_PRODUCER_WARPS;   // a multiple of the stage count
+constexpr int NACC = GRWS_TC5_NACC;                  // accumulator buffers in tensor memory
 constexpr int NUM_EPILOGUE = 128;
-constexpr int EPILOGUE_WARP0 = 0;                        // four warps; warp % 4 is its TMEM lane quarter
+constexpr int EPILOGUE_WARP0 = 0;                    // four warps; warp % 4 is its TMEM lane quarter
 constexpr int MMA_WARP = EPILOGUE_WARP0 + 4;
-constexpr int TMA_WARP = MMA_WARP + 1;
-#ifndef GRWS_TC5_META_WARPS
-#define GRWS_TC5_META_WARPS 1
-#endif
-constexpr int NUM_META_WARPS = GRWS_TC5_META_WARPS;     // they take the stages round-robin
-constexpr int PRODUCER_WARP0 = TMA_WARP + NUM_META_WARPS;
-#ifndef GRWS_TC5_MMA_PHYS_WARP
-#define GRWS_TC5_MMA_PHYS_WARP 4
-#endif
-static_assert(GRWS_TC5_MMA_PHYS_WARP >= 4, "warps 0-3 are the epilogue (their index is their TMEM lane quarter)");
+constexpr int WALK_WARP = MMA_WARP + 1;
+constexpr int PRODUCER_WARP0 = WALK_WARP + 1;
+constexpr int NUM_PRODUCER_WARPS = GRWS_TC5_STAGES;  // one per ring slot
 constexpr int NUM_THREADS = (PRODUCER_WARP0 + NUM_PRODUCER_WARPS) * 32;
 static_assert(EPILOGUE_WARP0 % 4 == 0, "epilogue warps must start at a multiple of four");
 constexpr int64_t SPLIT256_OPERAND_BYTES = 8ll << 20;   // dense operand size above which width 256 runs as two 128-column passes
-constexpr long long WAIT_LIMIT_CYCLES = 3000000000ll; // a wait gives up after about 1.5-2.5 s of SM clocks
+constexpr int LONG_WINDOW_SHIFT = 4;                 // a cut inside a window of at most chunk >> 4 tiles moves to the window start
+constexpr long long WAIT_LIMIT_CYCLES = 3000000000ll;   // default: a wait gives up after about 1.5-2.5 s of SM clocks
 
+// status codes: which wait ran out (the first four) / an injected failure of the self-test build
 enum : int { ST_OK = 0, ST_TIMEOUT_FULL = 1, ST_TIMEOUT_EMPTY = 2, ST_TIMEOUT_ACC = 3, ST_TIMEOUT_META = 4 };
+
+// experiment knobs of the profiling build (GRWS_TC5_SKIP); the product kernel compiles them out
+enum : int { SKIP_MMA = 1, SKIP_GATHER = 2, SKIP_STORE = 4, SKIP_TILES = 8, SKIP_ONE_ARRIVE = 16 };
 
 struct Params {
     const int64_t *window_offset;
@@ -114,14 +94,15 @@ struct Params {
     const void *B;
     void *C;
     float *partial;
-    int *status;
+    int *status;      // this call's status word (start of scratch)
+    int *sticky;      // per-device word that keeps the worst status since it was last read (may be null)
     int *split_count; // [grid]: pieces of the split window that starts in CTA k which are finished (zeroed before the launch)
     int64_t W, N, ldb, ldc;
     int c_dtype;
     int is_bf16;
-    int lw_shift;     // a cut inside a window of at most chunk >> lw_shift tiles moves to the window start
-    int skip;         // experiment knob (GRWS_TC5_SKIP): 1 = issue no MMAs, 2 = gather nothing, 4 = no output stores
-    long long *dbg;   // optional [grid][16] cycle counters (wait time per role), null when not profiling
+    int skip;         // profiling build only
+    long long wait_limit;   // SM clocks after which a barrier wait gives up
+    long long *dbg;   // profiling build: [grid][16] cycle counters (wait time per role) + a stage timeline
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -135,76 +116,84 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
-// adds to the bytes the current phase waits for, without arriving
-__device__ __forceinline__ void mbar_expect_tx_only(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
-#ifdef GRWS_TC5_WAIT_HINT_NS
-    // the hint lets the hardware keep the thread suspended for up to that long before it reports failure
-    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                 : "=r"(ok) : "r"(bar), "r"(parity), "r"((uint32_t)GRWS_TC5_WAIT_HINT_NS) : "memory");
-#else
     asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
                  : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-#endif
     return ok;
 }
-// bounded wait: gives up after WAIT_LIMIT_CYCLES SM clocks or when another role already aborted.
+// bounded wait: gives up after `limit` SM clocks or when another role already aborted.
 // (The SM clock is used because reading %globaltimer costs about a microsecond per read.)
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, long long limit) {
     if (mbar_try_wait(bar, parity)) return true;
     long long t0 = 0;
     for (uint32_t i = 0;; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
-#ifdef GRWS_TC5_BACKOFF
-        __nanosleep(GRWS_TC5_BACKOFF);
-#endif
         if ((i & 63u) == 63u) {
             if (*abort_flag) return false;
             const long long now = clock64();
             if (t0 == 0) t0 = now;
-            if (now - t0 > WAIT_LIMIT_CYCLES) return false;
+            if (now - t0 > limit) return false;
         }
     }
 }
+// the same wait without the abort test: used while draining after an abort
+__device__ __forceinline__ bool mbar_wait_drain(uint32_t bar, uint32_t parity, long long limit) {
+    const long long t0 = clock64();
+    for (uint32_t i = 0;; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 63u) == 63u && clock64() - t0 > limit) return false;
+    }
+}
 // wait that adds its duration to `acc` in the profiling build of the kernel
-__device__ unsigned long long g_prof_tries[8];     // profiling build: failed try_waits per role
 template <bool PROF>
-__device__ __forceinline__ bool mbar_wait_t(uint32_t bar, uint32_t parity, volatile int *abort_flag, long long &acc, int role = 0) {
+__device__ __forceinline__ bool mbar_wait_t(uint32_t bar, uint32_t parity, volatile int *abort_flag, long long limit, long long &acc, int role = 0) {
+    (void)role;
     if constexpr (PROF) {
+        // (a try_wait may itself suspend the thread until the phase completes, so even a wait whose
+        // first try succeeds has to be timed)
         const long long t0 = clock64();
-        unsigned long long tries = 0;
-        bool ok = false;
-        for (; tries < 100000000ull; ++tries) {
-            if (mbar_try_wait(bar, parity)) { ok = true; break; }
-#ifdef GRWS_TC5_BACKOFF
-            __nanosleep(GRWS_TC5_BACKOFF);
-#endif
-        }
+        const bool ok = mbar_wait(bar, parity, abort_flag, limit);
         acc += clock64() - t0;
-        if (tries) atomicAdd(&g_prof_tries[role], tries);
-        (void)abort_flag;
         return ok;
     } else {
-        return mbar_wait(bar, parity, abort_flag);
+        (void)acc;
+        return mbar_wait(bar, parity, abort_flag, limit);
     }
 }
 // timeline of the first stages of CTA 0 (profiling build): event e of stage `it`
 template <bool PROF> __device__ __forceinline__ void prof_mark(long long *dbg, uint32_t it, int e) {
+#ifdef GRWS_TC5_TIMELINE
     if constexpr (PROF) { if (dbg && blockIdx.x == 0 && it < 64) dbg[12288 + it * 8 + e] = clock64(); }
+#else
+    (void)dbg; (void)it; (void)e;
+#endif
 }
 template <bool PROF> __device__ __forceinline__ long long prof_clock() {
     if constexpr (PROF) return clock64(); else return 0;
+}
+// clock reads inside the per-stage loops: only in the timeline build (they slow the loops down)
+template <bool PROF> __device__ __forceinline__ long long prof_fine() {
+#ifdef GRWS_TC5_TIMELINE
+    if constexpr (PROF) return clock64();
+#endif
+    return 0;
 }
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar, uint64_t pol) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
                  ::"r"(dst), "l"(src), "r"(bytes), "r"(bar), "l"(pol) : "memory");
 }
+// bulk store of a contiguous piece of shared memory to global memory (both 16-byte aligned)
+__device__ __forceinline__ void bulk_s2g(void *dst, uint32_t src, uint32_t bytes, uint64_t pol) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group.L2::cache_hint [%0], [%1], %2, %3;"
+                 ::"l"(dst), "r"(src), "r"(bytes), "l"(pol) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 // TMA gather of four rows of the dense operand (tile::gather4): 64 features of rows r0..r3 land as
 // four consecutive 128-byte lines, already permuted for the 128-byte-swizzle operand layout.  A
 // negative or too large row id is out of bounds and reads zeros.
@@ -242,11 +231,26 @@ __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+// barrier 1 of the CTA for the 128 epilogue threads
+__device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+// the same barrier with an OR over every thread's flag: all 128 threads get the same answer
+__device__ __forceinline__ bool epilogue_sync_or(bool flag) {
+    uint32_t r;
+    asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbar.red.or.pred p, 1, 128, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(r) : "r"(flag ? 1u : 0u) : "memory");
+    return r != 0;
+}
 
 __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
     asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
                  "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
                  ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// the same with the accumulate flag fixed to "add to the accumulator" (no predicate to compute)
+__device__ __forceinline__ void umma_f16_acc(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.eq.u32 p, 0, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc) : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
@@ -333,8 +337,16 @@ struct Walker {
     __device__ __forceinline__ bool tail() const { return !(seg_s > a) && seg_e < b; }
 };
 
+// What the walker warp tells the producers about one stage: its first tile and its command word.
+struct __align__(16) StageDesc {
+    int64_t t0;
+    uint32_t cmd, pad;
+};
+constexpr int DESC_BATCHES = 8;                      // descriptor ring: batches of one descriptor per producer
+
 struct SharedStorage {
-    uint64_t full_g[16], empty_g[16], full_m[64], empty_m[64], acc_full[NACC], acc_empty[NACC];
+    uint64_t full_g[16], empty_g[16], full_m[48], desc_full[DESC_BATCHES], desc_empty[DESC_BATCHES], acc_full[NACC], acc_empty[NACC], drain;
+    StageDesc desc[DESC_BATCHES * GRWS_TC5_STAGES];
     uint32_t tmem_base;
     int abort_flag;
     int last_piece;       // epilogue: this CTA finished the last piece of a split window
@@ -348,22 +360,27 @@ template <int NH> struct Cfg {
 #endif
     static constexpr int kCtasPerSm = (NH == 1) ? GRWS_TC5_CTAS_PER_SM : 1;
     static constexpr int kStages = GRWS_TC5_STAGES;
-    // tile / column-id slots: the TMA warp runs kMeta - kStages stages ahead of the data it has
-    // already landed, which has to cover the HBM latency of the tile stream
-#ifndef GRWS_TC5_META_AHEAD
-#define GRWS_TC5_META_AHEAD 6
+    // tile / column-id slots per producer: the tiles of a producer's stage n + kMetaDepth - 1 are
+    // requested while it gathers for stage n, i.e. (kMetaDepth - 1) * kStages stages ahead of the
+    // MMAs, which has to cover the HBM latency of the tile stream
+#ifndef GRWS_TC5_META_DEPTH
+#define GRWS_TC5_META_DEPTH 2
 #endif
-    static constexpr int kMeta = kStages + ((NH == 1) ? GRWS_TC5_META_AHEAD : 16) * 8 / STAGE_TILES;
+    static constexpr int kMetaDepth = (NH == 1) ? GRWS_TC5_META_DEPTH : 3;
+    static constexpr int kMeta = kStages * kMetaDepth;
     static constexpr int kStageBytes = MMAS_PER_STAGE * NH * A_MMA_BYTES;
     static constexpr int kAccCols = 16 * NH;
     static constexpr int kTmemCols = (NACC * kAccCols) < 32 ? 32 : NACC * kAccCols;   // 64 or 128: powers of two
-    static_assert(kStages <= 16 && kMeta <= 64, "barrier arrays in SharedStorage");
-    static constexpr size_t kSmem = 1024 + sizeof(SharedStorage) + 16 + (size_t)kStages * kStageBytes + (size_t)kMeta * META_BYTES;
+    // one window of 16-bit output rows, staged for the bulk store: [16 rows][128 * NH features]
+    static constexpr int kStagingBytes = TILE_ROWS * SLAB * NH * 2;
+    static_assert(kStages <= 16 && kMeta <= 48, "barrier arrays in SharedStorage");
+    static constexpr size_t kSmem = 1024 + sizeof(SharedStorage) + 16 + (size_t)kStages * kStageBytes + (size_t)kMeta * META_BYTES + kStagingBytes;
 };
 
 __device__ __forceinline__ void raise(Params const &prm, SharedStorage *ss, int code) {
     ss->abort_flag = 1;
     atomicMax(prm.status, code);
+    if (prm.sticky) atomicMax(prm.sticky, code);
 }
 
 // The two rare paths of the epilogue live in functions of their own (not inlined), so that their
@@ -434,20 +451,25 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
     // the swizzled operand atoms must start on 1024-byte boundaries
     uint8_t *ring_g = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t *ring_m = ring_g + (size_t)C::kStages * C::kStageBytes;
-    SharedStorage *ss = reinterpret_cast<SharedStorage *>(ring_m + (size_t)C::kMeta * META_BYTES);
+    uint8_t *staging = ring_m + (size_t)C::kMeta * META_BYTES;
+    SharedStorage *ss = reinterpret_cast<SharedStorage *>(staging + C::kStagingBytes);
 
-    // role index of this warp: the hardware warp GRWS_TC5_MMA_PHYS_WARP trades places with the
-    // MMA role's default slot, which decides which other roles share a scheduler with the MMA issuer
     // the warp index is taken from lane 0 so that the compiler knows it is the same in all lanes:
     // everything derived from it (role, barrier and ring addresses) can live in uniform registers
-    const int phys_warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
-    const int warp = phys_warp == GRWS_TC5_MMA_PHYS_WARP ? MMA_WARP : (phys_warp == MMA_WARP ? GRWS_TC5_MMA_PHYS_WARP : phys_warp);
+    const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
     const int64_t W = prm.W;
+#ifndef GRWS_TC5_BUILD_SKIP
+#define GRWS_TC5_BUILD_SKIP 0                      // experiment builds leave parts of the work out (SKIP_* bits)
+#endif
+    const int skip = PROF ? prm.skip : GRWS_TC5_BUILD_SKIP;   // folds to zero in the product kernel
+    const long long limit = prm.wait_limit;
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < C::kStages; ++i) { mbar_init(smem_u32(&ss->full_g[i]), 1); mbar_init(smem_u32(&ss->empty_g[i]), 1); }
-        for (int i = 0; i < C::kMeta; ++i) { mbar_init(smem_u32(&ss->full_m[i]), 1); mbar_init(smem_u32(&ss->empty_m[i]), 1); }
+        for (int i = 0; i < C::kMeta; ++i) mbar_init(smem_u32(&ss->full_m[i]), 1);
+        for (int i = 0; i < DESC_BATCHES; ++i) { mbar_init(smem_u32(&ss->desc_full[i]), 1); mbar_init(smem_u32(&ss->desc_empty[i]), C::kStages); }
         for (int i = 0; i < NACC; ++i) { mbar_init(smem_u32(&ss->acc_full[i]), 1); mbar_init(smem_u32(&ss->acc_empty[i]), NUM_EPILOGUE / 32); }
+        mbar_init(smem_u32(&ss->drain), 1);
         ss->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -461,8 +483,7 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
     const uint32_t tmem_base = ss->tmem_base;
     volatile int *abort_flag = &ss->abort_flag;
 
-    const bool is_meta = warp >= TMA_WARP && warp < TMA_WARP + NUM_META_WARPS;
-    if (is_meta || (warp >= EPILOGUE_WARP0 && warp < MMA_WARP)) {
+    if (warp == WALK_WARP || (warp >= EPILOGUE_WARP0 && warp < MMA_WARP)) {
         // ---- the two roles that walk the window structure: this CTA's tile range [s, e)
         const int64_t T = __ldg(prm.window_offset + W);
         const int64_t G = gridDim.x;
@@ -470,305 +491,311 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
         chunk = (chunk + 1) & ~int64_t(1);
         if (chunk < 2) chunk = 2;
         // a cut inside a window of at most chunk/16 tiles moves back to that window's start, so
-        // only long windows are ever split between CTAs (tile counts stay balanced within chunk >> lw_shift)
-        const int64_t long_window = chunk >> prm.lw_shift;
+        // only long windows are ever split between CTAs (tile counts stay balanced within chunk / 16)
+        const int64_t long_window = chunk >> LONG_WINDOW_SHIFT;
         int64_t w_first, s, e;
         warp_cut_pair(prm.window_offset, W, T, blockIdx.x, G, chunk, long_window, lane, &s, &e, &w_first);
         Walker wk;
         wk.init(prm.window_offset, W, s, e, blockIdx.x == 0 ? 0 : w_first, lane);
 
-        if (is_meta) {
-            // -------------------------------------------------------------- TMA producer
-            const uint32_t meta_id = (uint32_t)(warp - TMA_WARP);
-            // streams tile values and column ids of every stage and tells the other roles, through
-            // the command word of the stage, what the stage holds
-            const uint64_t pol = policy_stream();
+        if (warp == WALK_WARP) {
+            // -------------------------------------------------------------- walker
+            // Walks this CTA's windows and writes one descriptor per stage (first tile, tile count,
+            // first / last stage of its window segment) into a small ring; the producers, which
+            // take the stages round-robin, fetch tiles, column ids and rows from the descriptors.
+            // A batch is one descriptor per producer and is published with one barrier arrive.
             uint32_t it = 0;
             bool ok = true;
-            long long w_empty_m = 0;
+            long long w_desc = 0, t_walk = 0;
             const long long t_start = prof_clock<PROF>();
-#if GRWS_TC5_SPAN
-            static_assert(NUM_META_WARPS == 1, "stages that span windows are packed by one warp");
-            // K-steps are packed into stages across window segments; a stage is published (command
-            // word written, barrier arrived on) when it is full or the CTA's range ends
-            uint32_t cmdw = 0, slot = 0;
-            int stage_k = 0;
-            while (ok && wk.next_segment(lane)) {
-                int64_t t0 = wk.seg_s;
-                bool first = true;
-                while (ok && t0 < wk.seg_e) {
-                    if (stage_k == 0) {
-                        slot = it % C::kMeta;
-                        const uint32_t ph = (it / C::kMeta) & 1u;
-                        if (lane == 0) ok = mbar_wait_t<PROF>(smem_u32(&ss->empty_m[slot]), ph ^ 1u, abort_flag, w_empty_m, 5);
-                        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-                        if (!ok) { if (lane == 0) raise(prm, ss, ST_TIMEOUT_META); break; }
-                    }
-                    const int n = (int)min(wk.seg_e - t0, (int64_t)(MMAS_PER_STAGE - stage_k) * 2);    // tiles placed now
-                    const int ks = (n + 1) >> 1;
-                    uint8_t *dst = ring_m + (size_t)slot * META_BYTES;
-                    const uint32_t bar = smem_u32(&ss->full_m[slot]);
-                    if (n & 1) {        // the segment ends on a first tile: the K-step's second tile multiplies as zeros
-                        if (lane < 16)
-                            *reinterpret_cast<uint4 *>(dst + (size_t)(stage_k * 2 + n) * TILE_BYTES + lane * 16) = make_uint4(0u, 0u, 0u, 0u);
-                        fence_async_smem();
-                        __syncwarp();
-                    }
-                    // flags: the piece's first K-step opens the segment, its last one may close it
-                    cmdw |= (first ? KS_FIRST : 0u) << (4 + 3 * stage_k);
-                    cmdw |= ((t0 + n == wk.seg_e ? KS_LAST : 0u) | ((n & 1) ? KS_SINGLE : 0u)) << (4 + 3 * (stage_k + ks - 1));
-                    const bool full = stage_k + ks == MMAS_PER_STAGE;
-                    if (elect_one()) {
-                        if (!(prm.skip & 8)) {
-                            mbar_expect_tx_only(bar, (uint32_t)n * (TILE_BYTES + TILE_COLS * 4));
-                            bulk_g2s(smem_u32(dst + (size_t)stage_k * 2 * TILE_BYTES), static_cast<const uint8_t *>(prm.vals) + t0 * TILE_BYTES,
-                                     (uint32_t)n * TILE_BYTES, bar, pol);
-                            bulk_g2s(smem_u32(dst + META_TILE_BYTES + (size_t)stage_k * 2 * TILE_COLS * 4), prm.cols + t0 * TILE_COLS,
-                                     (uint32_t)n * TILE_COLS * 4, bar, pol);
-                        }
-                        if (full) {                                // publish the stage
-                            *reinterpret_cast<volatile uint32_t *>(dst + META_TILE_BYTES + META_COL_BYTES) = (uint32_t)MMAS_PER_STAGE | cmdw;
-                            mbar_arrive(bar);                      // release: publishes the command
-                            prof_mark<PROF>(prm.dbg, it, 0);
-                        }
-                    }
-                    stage_k += ks;
-                    t0 += n;
-                    first = false;
-                    if (full) {
-                        ++it;
-                        stage_k = 0;
-                        cmdw = 0;
-                    }
+            // all lanes call; lane 0 writes
+            auto push = [&](int64_t t0, uint32_t cmd) {
+                const uint32_t pos = it % C::kStages, batch = it / C::kStages, bslot = batch % DESC_BATCHES;
+                if (pos == 0) {
+                    if (lane == 0) ok = mbar_wait_t<PROF>(smem_u32(&ss->desc_empty[bslot]), ((batch / DESC_BATCHES) & 1u) ^ 1u, abort_flag, limit, w_desc, 5);
+                    ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+                    if (!ok) { if (lane == 0) raise(prm, ss, ST_TIMEOUT_META); return; }
                 }
-            }
-            if (ok && stage_k > 0) {                               // the last, partly filled stage
-                __syncwarp();
-                if (elect_one()) {
-                    *reinterpret_cast<volatile uint32_t *>(ring_m + (size_t)slot * META_BYTES + META_TILE_BYTES + META_COL_BYTES) = (uint32_t)stage_k | cmdw;
-                    mbar_arrive(smem_u32(&ss->full_m[slot]));
+                if (lane == 0) {
+                    StageDesc *d = &ss->desc[bslot * C::kStages + pos];
+                    d->t0 = t0;
+                    d->cmd = cmd;
+                    if (pos == C::kStages - 1) {
+                        // self-test of the bounded waits (profiling build): one batch is never
+                        // published; nothing was copied for it, so every role runs into its limit
+                        if (!(PROF && (skip & SKIP_ONE_ARRIVE) && batch == 1 && blockIdx.x == 0))
+                            mbar_arrive(smem_u32(&ss->desc_full[bslot]));    // release: publishes the batch
+                    }
                 }
                 ++it;
-            }
-#else
-            while (ok && wk.next_segment(lane)) {
-                for (int64_t t0 = wk.seg_s; ok && t0 < wk.seg_e; t0 += STAGE_TILES, ++it) {
-                    if (it % NUM_META_WARPS != meta_id) continue;      // another meta warp's stage
-                    const uint32_t slot = it % C::kMeta, ph = (it / C::kMeta) & 1u;
+            };
+            for (;;) {
+                const long long tw0 = prof_fine<PROF>();
+                const bool more = ok && wk.next_segment(lane);
+                t_walk += prof_fine<PROF>() - tw0;
+                if (!more) break;
+                for (int64_t t0 = wk.seg_s; ok && t0 < wk.seg_e; t0 += STAGE_TILES) {
                     const int ntiles = (int)min((int64_t)STAGE_TILES, wk.seg_e - t0);
-                    if (lane == 0) ok = mbar_wait_t<PROF>(smem_u32(&ss->empty_m[slot]), ph ^ 1u, abort_flag, w_empty_m, 5);
-                    ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-                    if (ok && (ntiles & 1)) {
-                        // an odd tile count leaves the second tile of the last K-step without data:
-                        // zero it (the MMA multiplies it with zero rows, which must not meet NaNs)
-                        if (lane < 16)
-                            *reinterpret_cast<uint4 *>(ring_m + (size_t)slot * META_BYTES + (size_t)ntiles * TILE_BYTES + lane * 16) = make_uint4(0u, 0u, 0u, 0u);
-                        fence_async_smem();
-                        __syncwarp();
-                    }
-                    __syncwarp();
-                    if (elect_one()) {
-                        if (ok) {
-                            const uint32_t bar = smem_u32(&ss->full_m[slot]);
-                            uint8_t *dst = ring_m + (size_t)slot * META_BYTES;
-                            *reinterpret_cast<volatile uint32_t *>(dst + META_TILE_BYTES + META_COL_BYTES) =
-                                (uint32_t)ntiles | (t0 == wk.seg_s ? CMD_FIRST : 0u) | (t0 + STAGE_TILES >= wk.seg_e ? CMD_LAST : 0u);
-                            if (prm.skip & 8) {
-                                mbar_arrive(bar);
-                            } else {
-                            mbar_expect_tx(bar, (uint32_t)ntiles * (TILE_BYTES + TILE_COLS * 4));   // release: publishes the command
-                            bulk_g2s(smem_u32(dst), static_cast<const uint8_t *>(prm.vals) + t0 * TILE_BYTES,
-                                     (uint32_t)ntiles * TILE_BYTES, bar, pol);
-                            bulk_g2s(smem_u32(dst + META_TILE_BYTES), prm.cols + t0 * TILE_COLS,
-                                     (uint32_t)ntiles * TILE_COLS * 4, bar, pol);
-                            }
-                            prof_mark<PROF>(prm.dbg, it, 0);
-                        } else {
-                            raise(prm, ss, ST_TIMEOUT_META);
-                        }
-                    }
-                    ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+                    push(t0, (uint32_t)ntiles | (t0 == wk.seg_s ? CMD_FIRST : 0u) | (t0 + STAGE_TILES >= wk.seg_e ? CMD_LAST : 0u));
                 }
             }
-#endif
-            if (lane == 0 && meta_id == 0) {   // one end marker per gather slot; the MMA warp stops at the first
-                for (int j = 0; ok && j < C::kStages; ++j, ++it) {
-                    const uint32_t slot = it % C::kMeta, ph = (it / C::kMeta) & 1u;
-                    ok = mbar_wait_t<PROF>(smem_u32(&ss->empty_m[slot]), ph ^ 1u, abort_flag, w_empty_m);
-                    if (ok) {
-                        *reinterpret_cast<volatile uint32_t *>(ring_m + (size_t)slot * META_BYTES + META_TILE_BYTES + META_COL_BYTES) = CMD_END;
-                        mbar_arrive(smem_u32(&ss->full_m[slot]));
-                    } else {
-                        raise(prm, ss, ST_TIMEOUT_META);
-                    }
-                }
+            // one end marker per producer (the MMA warp stops at the first), then the rest of the batch
+            for (int j = 0; ok && (j < C::kStages || it % C::kStages != 0); ++j) push(0, CMD_END);
+            if (PROF && prm.dbg && lane == 0) {
+                prm.dbg[blockIdx.x * 16 + 0] = w_desc; prm.dbg[blockIdx.x * 16 + 1] = prof_clock<PROF>() - t_start;
+                prm.dbg[blockIdx.x * 16 + 15] = t_walk;
             }
-            if (PROF && prm.dbg && lane == 0 && meta_id == 0) { prm.dbg[blockIdx.x * 16 + 0] = w_empty_m; prm.dbg[blockIdx.x * 16 + 1] = prof_clock<PROF>() - t_start; }
         } else {
             // -------------------------------------------------------------- epilogue warps
             const uint64_t pol = policy_stream();
             const int q = warp & 3;                        // TMEM lane quarter this warp may read
             uint32_t ai = 0;
-            bool ok = true;
             long long w_af = 0;
+            const long long t_epi0 = prof_clock<PROF>();
+            // 16-bit outputs go through shared memory: every thread holds one feature of the 16 rows
+            // (a tensor-memory lane), the window's rows are assembled in `staging` and leave as one
+            // bulk store when the output rows are contiguous (ldc == N), else one per row
+            const bool staged = prm.c_dtype != GRWS_F32 && !(skip & SKIP_STORE);
+            const int64_t row_bytes = (int64_t)SLAB * NH * 2;
             // Windows without tiles produce zero rows.  They are dealt to all CTAs here, while the
             // pipeline fills, instead of being written by whichever CTA's tile range they border:
             // a run of empty windows (padded blocks, isolated nodes) would serialise on that one CTA.
-            if (!(prm.skip & 4)) zero_fill_empty_windows<NH>(prm.window_offset, prm.C, prm.ldc, prm.c_dtype, W, q, lane);
-            while (ok && wk.next_segment(lane)) {
+            if (!(skip & SKIP_STORE)) zero_fill_empty_windows<NH>(prm.window_offset, prm.C, prm.ldc, prm.c_dtype, W, q, lane);
+            for (;;) {
+                const bool more = wk.next_segment(lane);
+                if (!more) break;                          // the same in all four warps: they walk the same ranges
                 const int64_t w = wk.window();
-                const bool nonempty = wk.seg_e > wk.seg_s;
-                if (!nonempty) continue;                   // zero rows were written above
+                if (wk.seg_e <= wk.seg_s) continue;        // zero rows were written above
                 uint32_t v[NH][16];
-                if (nonempty) {
-                    const uint32_t buf = ai % NACC, aph = (ai / NACC) & 1u;
-                    ++ai;
-                    // one polling lane per warp: threads spinning on a barrier slow every other
-                    // barrier operation of the SM down
-                    if (lane == 0) ok = mbar_wait_t<PROF>(smem_u32(&ss->acc_full[buf]), aph, abort_flag, w_af, 4);
-                    ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-                    if (!ok) { if (lane == 0) raise(prm, ss, ST_TIMEOUT_ACC); break; }
-                    tc_fence_after();
-#pragma unroll
-                    for (int h = 0; h < NH; ++h)
-                        tmem_ld16(tmem_base + ((uint32_t)(32 * q) << 16) + buf * C::kAccCols + h * 16, v[h]);
-                    tmem_ld_wait();
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(smem_u32(&ss->acc_empty[buf]));
-                } else {
-#pragma unroll
-                    for (int h = 0; h < NH; ++h)
-#pragma unroll
-                        for (int r = 0; r < 16; ++r) v[h][r] = 0u;
+                const uint32_t buf = ai % NACC, aph = (ai / NACC) & 1u;
+                ++ai;
+                // One thread polls for all four warps (threads spinning on a barrier slow every other
+                // barrier operation of the SM down); it also makes sure that the previous window's
+                // bulk store has finished reading `staging`.  All four warps then meet and leave
+                // together when the wait ran out or another role gave up: none may be left alone at a
+                // later barrier.
+                bool ok = true;
+                if (threadIdx.x == EPILOGUE_WARP0 * 32) {
+                    ok = mbar_wait_t<PROF>(smem_u32(&ss->acc_full[buf]), aph, abort_flag, limit, w_af, 4);
+                    if (!ok) raise(prm, ss, ST_TIMEOUT_ACC);
+                    bulk_wait_read0();
                 }
-                const bool partial = wk.head() || wk.tail();
+                if (epilogue_sync_or(!ok || *abort_flag != 0)) break;
+                tc_fence_after();
 #pragma unroll
-                for (int h = 0; h < NH; ++h) {
-                    const int64_t f = h * SLAB + 32 * q + lane;
-                    if (prm.skip & 4) {
-                    } else if (!partial) {
-                        const int64_t base = (w * TILE_ROWS) * prm.ldc + f;
+                for (int h = 0; h < NH; ++h)
+                    tmem_ld16(tmem_base + ((uint32_t)(32 * q) << 16) + buf * C::kAccCols + h * 16, v[h]);
+                tmem_ld_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&ss->acc_empty[buf]));
+                const bool partial = wk.head() || wk.tail();
+                if (skip & SKIP_STORE) {
+                } else if (!partial && staged) {
+#pragma unroll
+                    for (int h = 0; h < NH; ++h) {
+                        uint16_t *st = reinterpret_cast<uint16_t *>(staging) + h * SLAB + 32 * q + lane;
 #pragma unroll
                         for (int r = 0; r < 16; ++r) {
                             const float x = __uint_as_float(v[h][r]);
-                            const int64_t o = base + r * prm.ldc;
-                            if (prm.c_dtype == GRWS_F32) {
-                                asm volatile("st.global.L2::cache_hint.f32 [%0], %1, %2;" ::"l"(static_cast<float *>(prm.C) + o), "f"(x), "l"(pol) : "memory");
-                            } else {
-                                const uint16_t hbits = prm.c_dtype == GRWS_F16 ? __half_as_ushort(__float2half_rn(x))
-                                                                               : __bfloat16_as_ushort(__float2bfloat16_rn(x));
-                                asm volatile("st.global.L2::cache_hint.u16 [%0], %1, %2;" ::"l"(static_cast<uint16_t *>(prm.C) + o), "h"(hbits), "l"(pol) : "memory");
-                            }
+                            st[r * (SLAB * NH)] = prm.c_dtype == GRWS_F16 ? __half_as_ushort(__float2half_rn(x))
+                                                                         : __bfloat16_as_ushort(__float2bfloat16_rn(x));
                         }
-                    } else {
-                        float *slot = prm.partial + (2 * (int64_t)blockIdx.x + (wk.tail() ? 1 : 0)) * (TILE_ROWS * prm.N);
-#pragma unroll
-                        for (int r = 0; r < 16; ++r) slot[(int64_t)r * prm.N + f] = __uint_as_float(v[h][r]);
                     }
-                }
-                if (partial && !(prm.skip & 4)) {
+                    fence_async_smem();                    // the bulk store reads through the async proxy
+                    epilogue_sync();
+                    if (threadIdx.x == EPILOGUE_WARP0 * 32) {
+                        char *dst = static_cast<char *>(prm.C) + (w * TILE_ROWS) * prm.ldc * 2;
+                        if (prm.ldc == prm.N) {
+                            bulk_s2g(dst, smem_u32(staging), (uint32_t)(TILE_ROWS * row_bytes), pol);
+                        } else {
+#pragma unroll 1
+                            for (int r = 0; r < TILE_ROWS; ++r)
+                                bulk_s2g(dst + (int64_t)r * prm.ldc * 2, smem_u32(staging) + (uint32_t)(r * row_bytes), (uint32_t)row_bytes, pol);
+                        }
+                        bulk_commit();
+                    }
+                } else if (!partial) {
+#pragma unroll
+                    for (int h = 0; h < NH; ++h) {
+                        const int64_t base = (w * TILE_ROWS) * prm.ldc + h * SLAB + 32 * q + lane;
+#pragma unroll
+                        for (int r = 0; r < 16; ++r)
+                            asm volatile("st.global.L2::cache_hint.f32 [%0], %1, %2;"
+                                         ::"l"(static_cast<float *>(prm.C) + base + r * prm.ldc), "f"(__uint_as_float(v[h][r])), "l"(pol) : "memory");
+                    }
+                } else {
+#pragma unroll
+                    for (int h = 0; h < NH; ++h) {
+                        float *slot = prm.partial + (2 * (int64_t)blockIdx.x + (wk.tail() ? 1 : 0)) * (TILE_ROWS * prm.N) + h * SLAB + 32 * q + lane;
+#pragma unroll
+                        for (int r = 0; r < 16; ++r) slot[(int64_t)r * prm.N] = __uint_as_float(v[h][r]);
+                    }
                     // A window cut between CTAs: every holder of a piece counts itself on the counter of
                     // the CTA that holds the window's first tile, and the one that arrives last sums the
                     // pieces in CTA order (the same order whoever is last) and writes the rows.  Cuts
                     // inside a split window are never moved, so its pieces are exactly the CTAs
                     // a / chunk .. (b - 1) / chunk.
                     __threadfence();
-                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    epilogue_sync();
                     const int64_t k0 = wk.a / chunk, k_last = (wk.b - 1) / chunk;
-                    if (threadIdx.x == 0) {
+                    if (threadIdx.x == EPILOGUE_WARP0 * 32) {
                         const int old = atomicAdd(prm.split_count + k0, 1);
                         ss->last_piece = (old == (int)(k_last - k0)) ? 1 : 0;
                     }
-                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    epilogue_sync();
                     if (*reinterpret_cast<volatile int *>(&ss->last_piece)) sum_pieces<NH>(prm.partial, prm.N, prm.C, prm.ldc, prm.c_dtype, w, k0, k_last, q, lane);
                 }
             }
-            if (PROF && prm.dbg && threadIdx.x == EPILOGUE_WARP0 * 32) prm.dbg[blockIdx.x * 16 + 7] = w_af;
+            if (threadIdx.x == EPILOGUE_WARP0 * 32) bulk_wait0();      // this CTA's output stores are complete
+            if (PROF && prm.dbg && threadIdx.x == EPILOGUE_WARP0 * 32) { prm.dbg[blockIdx.x * 16 + 7] = w_af; prm.dbg[blockIdx.x * 16 + 14] = prof_clock<PROF>() - t_epi0; }
         }
     } else if (warp >= PRODUCER_WARP0) {
         // ------------------------------------------------------------------ gather producers
-        // Producer warps k*w .. k*w+k-1 own ring slot w (k = 1 by default) and fill every kStages-th
-        // stage, so the barrier polls and column-id reads of kStages stages overlap.  The rows are
-        // fetched by the TMA unit (tile::gather4: four consecutive slots x 64 features per copy,
-        // 32 copies per stage and slab), all issued by one elected lane in an unrolled loop: a copy
-        // issued per lane costs its warp ~220 cycles (the copies of different lanes go one after
-        // the other and each marshals its operands into uniform registers), a copy from the elected
-        // lane with warp-uniform operands ~70.  The copies complete on the stage's barrier.
-        constexpr int WARPS_PER_SLOT = NUM_PRODUCER_WARPS / Cfg<NH>::kStages;
-        constexpr int STAGE_OPS = MMAS_PER_STAGE * 8;                          // gather4 copies per stage and slab
-        static_assert(WARPS_PER_SLOT >= 1 && WARPS_PER_SLOT * Cfg<NH>::kStages == NUM_PRODUCER_WARPS, "producer warps per slot");
-        const uint64_t keep = policy_keep();
-        const int pwarp = warp - PRODUCER_WARP0;
-        const int member = pwarp % WARPS_PER_SLOT;            // the copies of a stage are dealt round-robin to the slot's warps
-        long long w_full_m = 0, w_empty_g = 0;
-        const uint32_t gs = (uint32_t)(pwarp / WARPS_PER_SLOT);
-        const uint32_t full_bar = smem_u32(&ss->full_g[gs]), empty_bar = smem_u32(&ss->empty_g[gs]);
-        const uint32_t dst_slot = smem_u32(ring_g + (size_t)gs * C::kStageBytes);
-        uint32_t gph = 0;
-        for (uint32_t it = gs;; it += C::kStages, gph ^= 1u) {
-            const uint32_t ms = it % C::kMeta, mph = (it / C::kMeta) & 1u;
-            // column ids and the command have landed
-            bool ok = true;
-            if (lane == 0) ok = mbar_wait_t<PROF>(smem_u32(&ss->full_m[ms]), mph, abort_flag, w_full_m, 3);
-            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-            if (!ok) { if (lane == 0) raise(prm, ss, ST_TIMEOUT_META); break; }
-            if (lane == 0) prof_mark<PROF>(prm.dbg, it, 1);
-            const uint8_t *meta = ring_m + (size_t)ms * META_BYTES;
-            const uint32_t cmd = *reinterpret_cast<const volatile uint32_t *>(meta + META_TILE_BYTES + META_COL_BYTES);
-            const bool end = (cmd & CMD_END) != 0;
-#if GRWS_TC5_SPAN
-            const int nmma = end ? 0 : (int)(cmd & CMD_COUNT);   // K-steps of the stage
-#else
-            const int ntiles = end ? 0 : (int)(cmd & CMD_COUNT);
-            const int nvalid = ntiles * TILE_COLS;               // slots that carry a column id
-            const int nmma = (ntiles + 1) >> 1;
-#endif
-            // the gather slot has been released by the MMA warp (it finished stage it - kStages)
-            if (lane == 0) ok = mbar_wait_t<PROF>(empty_bar, gph ^ 1u, abort_flag, w_empty_g, 2);
-            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-            if (!ok) { if (lane == 0) raise(prm, ss, ST_TIMEOUT_EMPTY); break; }
-            if (lane == 0) prof_mark<PROF>(prm.dbg, it, 2);
-            // ... which also frees the tile / column slot of that older stage for the TMA warp
-            if (lane == 0 && member == 0 && it >= (uint32_t)C::kStages) mbar_arrive(smem_u32(&ss->empty_m[(it - C::kStages) % C::kMeta]));
-            if (end) {                      // pass the end marker on to the MMA warp
-                if (lane == 0 && member == 0) mbar_arrive(full_bar);
-                break;
-            }
-            // bytes the K-steps of this stage bring in: 16 slots x 128 features x NH slabs each
-            if (lane == 0 && member == 0) {
-                if (prm.skip & 2) mbar_arrive(full_bar);          // experiment: no gathers, nothing to wait for
-                else mbar_expect_tx(full_bar, (uint32_t)(nmma * 16 * SLAB * 2 * NH));
-            }
-            // (K-step om, slot group og, feature half oh) of copy o: slots 4*og .. 4*og+3 of K-step om
-            // land in slot half og / 2, lines (4*og) % 8 .. +3 of the atom; slots past the last tile
-            // carry no column id and fetch row -1, which is out of bounds and reads zeros
-            __syncwarp();
-            if (elect_one() && !(prm.skip & 2)) {
-                constexpr int MAX_OPS = (STAGE_OPS + WARPS_PER_SLOT - 1) / WARPS_PER_SLOT;
+        // Producer warp w owns ring slot w and fills every kStages-th stage, so the barrier polls
+        // and column-id reads of kStages stages overlap.  The rows are fetched by the TMA unit
+        // (tile::gather4: four consecutive slots x 64 features per copy, 32 copies per stage and
+        // slab).  The whole role runs on one elected lane: a copy issued per lane costs its warp
+        // ~220 cycles (the copies of different lanes go one after the other and each marshals its
+        // operands into uniform registers).  The column ids of two K-steps are loaded into
+        // registers before their 16 copies are issued -- a shared-memory load between two copies
+        // cannot be moved across them and costs the chain ~45 cycles per copy instead of ~20 -- and
+        // the first batch is loaded while the ring slot is still being waited for.
+        const uint32_t gs = (uint32_t)(warp - PRODUCER_WARP0);
+        if (elect_one()) {
+            constexpr uint32_t D = (uint32_t)C::kMetaDepth;
+            const uint64_t keep = policy_keep(), stream_pol = policy_stream();
+            long long w_full_m = 0, w_empty_g = 0, w_desc = 0, t_meta = 0;
+            const long long t_prod0 = prof_clock<PROF>();
+            const uint32_t full_bar = smem_u32(&ss->full_g[gs]), empty_bar = smem_u32(&ss->empty_g[gs]);
+            const uint32_t dst_slot = smem_u32(ring_g + (size_t)gs * C::kStageBytes);
+            uint32_t gph = 0, armed_ph = 0;
+            bool armed = false;               // phase armed_ph of full_bar waits for copies of this warp
+            bool failed = false, seen_end = false;
+            uint32_t n_meta = 0;              // this producer's next stage whose tiles have not been requested yet
+            // Requests tiles and column ids of this producer's stage n_meta (descriptor batch n_meta)
+            // into its meta slot n_meta % D, and copies the command word there for the MMA thread.
+            auto request_tiles = [&]() {
+                const uint32_t bslot = n_meta % DESC_BATCHES;
+                if (!mbar_wait_t<PROF>(smem_u32(&ss->desc_full[bslot]), (n_meta / DESC_BATCHES) & 1u, abort_flag, limit, w_desc, 5)) {
+                    raise(prm, ss, ST_TIMEOUT_META);
+                    failed = true;
+                    return;
+                }
+                const long long tm0 = prof_fine<PROF>();
+                StageDesc d;
+                {
+                    const int4 raw = *reinterpret_cast<const int4 *>(&ss->desc[bslot * C::kStages + gs]);
+                    d.t0 = (int64_t)(((uint64_t)(uint32_t)raw.y << 32) | (uint32_t)raw.x);
+                    d.cmd = (uint32_t)raw.z;
+                }
+                mbar_arrive(smem_u32(&ss->desc_empty[bslot]));
+                const uint32_t mslot = gs * D + n_meta % D;
+                uint8_t *dst = ring_m + (size_t)mslot * META_BYTES;
+                const uint32_t bar = smem_u32(&ss->full_m[mslot]);
+                *reinterpret_cast<volatile uint32_t *>(dst + META_TILE_BYTES + META_COL_BYTES) = d.cmd;
+                ++n_meta;
+                if (d.cmd & CMD_END) {
+                    seen_end = true;
+                    mbar_arrive(bar);
+                    return;
+                }
+                const uint32_t ntiles = d.cmd & CMD_COUNT;
+                if (ntiles & 1u) {
+                    // An odd tile count leaves the second tile of the last K-step without data: its
+                    // values become zeros (the MMA multiplies them with zero rows, which must not
+                    // meet NaNs) and its column ids -1 (their rows are fetched as zeros).
 #pragma unroll
-                for (int j = 0; j < MAX_OPS; ++j) {
-                    const int o = member + j * WARPS_PER_SLOT;
-                    const int om = o >> 3, og = (o >> 1) & 3, oh = o & 1;
-                    if (o < STAGE_OPS && om < nmma) {
-                        const int s0 = 16 * om + 4 * og;
-                        int4 r = *reinterpret_cast<const int4 *>(meta + META_TILE_BYTES + s0 * 4);
-#if GRWS_TC5_SPAN
-                        if ((kstep_flags(cmd, om) & KS_SINGLE) && og >= 2) r = make_int4(-1, -1, -1, -1);
-#else
-                        if (s0 >= nvalid) r = make_int4(-1, -1, -1, -1);
-#endif
-                        const uint32_t off = (uint32_t)(om * NH * A_MMA_BYTES + (og >> 1) * A_SBO + oh * A_LBO + ((4 * og) & 7) * 128);
+                    for (int i = 0; i < TILE_BYTES / 16; ++i)
+                        *reinterpret_cast<uint4 *>(dst + (size_t)ntiles * TILE_BYTES + i * 16) = make_uint4(0u, 0u, 0u, 0u);
+                    *reinterpret_cast<int4 *>(dst + META_TILE_BYTES + (size_t)ntiles * TILE_COLS * 4) = make_int4(-1, -1, -1, -1);
+                    *reinterpret_cast<int4 *>(dst + META_TILE_BYTES + (size_t)ntiles * TILE_COLS * 4 + 16) = make_int4(-1, -1, -1, -1);
+                    fence_async_smem();
+                }
+                if (skip & SKIP_TILES) {
+                    mbar_arrive(bar);
+                } else {
+                    mbar_expect_tx(bar, ntiles * (TILE_BYTES + TILE_COLS * 4));
+                    bulk_g2s(smem_u32(dst), static_cast<const uint8_t *>(prm.vals) + d.t0 * TILE_BYTES, ntiles * TILE_BYTES, bar, stream_pol);
+                    bulk_g2s(smem_u32(dst + META_TILE_BYTES), prm.cols + d.t0 * TILE_COLS, ntiles * TILE_COLS * 4, bar, stream_pol);
+                }
+                t_meta += prof_fine<PROF>() - tm0;
+                prof_mark<PROF>(prm.dbg, gs + (n_meta - 1) * C::kStages, 0);
+            };
+            for (uint32_t j = 0; j < D && !seen_end && !failed; ++j) request_tiles();
+            for (uint32_t n = 0; !failed; ++n, gph ^= 1u) {
+                const uint32_t it = gs + n * C::kStages;
+                const uint32_t mslot = gs * D + n % D;
+                // tile values, column ids and the command have landed
+                if (!mbar_wait_t<PROF>(smem_u32(&ss->full_m[mslot]), (n / D) & 1u, abort_flag, limit, w_full_m, 3)) { raise(prm, ss, ST_TIMEOUT_META); break; }
+                prof_mark<PROF>(prm.dbg, it, 1);
+                const uint8_t *meta = ring_m + (size_t)mslot * META_BYTES;
+                const uint32_t cmd = *reinterpret_cast<const volatile uint32_t *>(meta + META_TILE_BYTES + META_COL_BYTES);
+                const bool end = (cmd & CMD_END) != 0;
+                const int nmma = end ? 0 : (int)((cmd & CMD_COUNT) + 1u) >> 1;
+                const int4 *ids = reinterpret_cast<const int4 *>(meta + META_TILE_BYTES);
+                int4 r[8];                                // slots of K-steps 0 and 1 (stale ids past the stage's last K-step are never used)
 #pragma unroll
-                        for (int h = 0; h < NH; ++h)
-                            tma_gather4(dst_slot + off + (uint32_t)(h * A_MMA_BYTES), &b_map, full_bar, h * SLAB + oh * 64, r.x, r.y, r.z, r.w, keep);
+                for (int g = 0; g < 8; ++g) r[g] = ids[g];
+                // The MMA warp has finished this producer's previous stage: its gather slot is free,
+                // and so is the meta slot that stage's tiles were in.
+                if (!mbar_wait_t<PROF>(empty_bar, gph ^ 1u, abort_flag, limit, w_empty_g, 2)) { raise(prm, ss, ST_TIMEOUT_EMPTY); break; }
+                armed = false;
+                prof_mark<PROF>(prm.dbg, it, 2);
+                if (end) {                      // pass the end marker on to the MMA warp
+                    mbar_arrive(full_bar);
+                    break;
+                }
+                if (skip & SKIP_GATHER) {       // experiment: nothing to wait for
+                    mbar_arrive(full_bar);
+                } else {
+                    // bytes the K-steps of this stage bring in: 16 slots x 128 features x NH slabs each
+                    mbar_expect_tx(full_bar, (uint32_t)(nmma * 16 * SLAB * 2 * NH));
+                    armed = true;
+                    armed_ph = gph;
+                    // copy (K-step m, slot group g, feature half oh): slots 4g .. 4g+3 of K-step m land in
+                    // slot half g / 2, lines (4g) % 8 .. +3 of the atom
+#pragma unroll
+                    for (int m0 = 0; m0 < MMAS_PER_STAGE; m0 += 2) {
+                        if (m0 > 0) {
+                            if (m0 >= nmma) break;
+#pragma unroll
+                            for (int g = 0; g < 8; ++g) r[g] = ids[m0 * 4 + g];
+                        }
+#pragma unroll
+                        for (int mm = 0; mm < 2; ++mm) {
+                            if (m0 + mm < nmma) {
+#pragma unroll
+                                for (int g = 0; g < 4; ++g) {
+                                    const int4 rr = r[mm * 4 + g];
+#pragma unroll
+                                    for (int oh = 0; oh < 2; ++oh) {
+                                        const uint32_t off = (uint32_t)((m0 + mm) * NH * A_MMA_BYTES + (g >> 1) * A_SBO + oh * A_LBO + ((4 * g) & 7) * 128);
+#pragma unroll
+                                        for (int h = 0; h < NH; ++h)
+                                            tma_gather4(dst_slot + off + (uint32_t)(h * A_MMA_BYTES), &b_map, full_bar, h * SLAB + oh * 64, rr.x, rr.y, rr.z, rr.w, keep);
+                                    }
+                                }
+                            }
+                        }
                     }
                 }
+                prof_mark<PROF>(prm.dbg, it, 3);
+                // the meta slot of stage n - 1 takes the tiles of stage n - 1 + D
+                if (n >= 1 && !seen_end) request_tiles();
             }
-            __syncwarp();
-            if (lane == 0) prof_mark<PROF>(prm.dbg, it, 3);
+            if (*abort_flag) {
+                // aborted with copies of this thread possibly in flight: wait (bounded) until they
+                // have landed, the CTA is about to give its shared memory back
+                if (armed) (void)mbar_wait_drain(full_bar, armed_ph, limit);
+                for (uint32_t j = 1; j <= D && j <= n_meta; ++j) {
+                    const uint32_t nj = n_meta - j;
+                    (void)mbar_wait_drain(smem_u32(&ss->full_m[gs * D + nj % D]), (nj / D) & 1u, limit);
+                }
+            }
+            if (PROF && prm.dbg && gs == 0) { prm.dbg[blockIdx.x * 16 + 2] = w_full_m; prm.dbg[blockIdx.x * 16 + 3] = w_empty_g; prm.dbg[blockIdx.x * 16 + 13] = w_desc; prm.dbg[blockIdx.x * 16 + 5] = prof_clock<PROF>() - t_prod0; (void)t_meta; }
         }
-        if (PROF && prm.dbg && threadIdx.x == PRODUCER_WARP0 * 32) { prm.dbg[blockIdx.x * 16 + 2] = w_full_m; prm.dbg[blockIdx.x * 16 + 3] = w_empty_g; }
+        __syncwarp();
     } else if (warp == MMA_WARP) {
         // ------------------------------------------------------------------ MMA issuer (one thread)
         if (elect_one()) {
@@ -778,102 +805,75 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
             const uint64_t a_desc0 = smem_desc(smem_u32(ring_g), A_LBO, A_SBO, 2);
             const uint64_t b_desc0 = smem_desc(smem_u32(ring_m), TILE_BYTES, 128, 0);
             uint32_t ai = 0, buf = 0;
-            long long w_acc = 0, w_fm = 0, w_fg = 0, t_issue = 0, t_commit = 0, t_cmd = 0, t_fence = 0;
+            long long w_acc = 0, w_fg = 0;
             const long long t_mark = prof_clock<PROF>();
-            uint32_t it = 0, gs = 0, gph = 0, ms = 0;
-            for (;; ++it) {
-                // The producers arrive on full_g only after they have seen full_m of the same stage,
-                // so this one wait also covers the tile values and the command word.
-                if (!mbar_wait_t<PROF>(smem_u32(&ss->full_g[gs]), gph, abort_flag, w_fg, 1)) { raise(prm, ss, ST_TIMEOUT_FULL); break; }
-                prof_mark<PROF>(prm.dbg, it, 5);
-                const long long tc0 = prof_clock<PROF>();
-                const uint32_t cmd = *reinterpret_cast<const volatile uint32_t *>(ring_m + ms * META_BYTES + META_TILE_BYTES + META_COL_BYTES);
-                if (cmd & CMD_END) break;
-                if (PROF) t_cmd += prof_clock<PROF>() - tc0 + (long long)(cmd & 0);
-#if GRWS_TC5_SPAN
-                const int nmma = (int)(cmd & CMD_COUNT);
-                const long long tf0 = prof_clock<PROF>();
-                tc_fence_after();
-                const long long ti0 = prof_clock<PROF>();
-                t_fence += ti0 - tf0;
-                const uint64_t ad = a_desc0 + (uint64_t)(gs * (C::kStageBytes >> 4));
-                const uint64_t bd = b_desc0 + (uint64_t)(ms * (META_BYTES >> 4));
-                // first pass: take the accumulator buffers of the segments that start in this stage
-                // (at most four, and the buffer of the fourth was released by a segment that ended in an
-                // earlier stage, so waiting for all of them up front cannot block on this stage's own
-                // MMAs); second pass: the MMAs and commits as one straight-line sequence
-                bool alive = true;
-                uint32_t dt[MMAS_PER_STAGE], kbuf[MMAS_PER_STAGE];
+            constexpr uint32_t D = (uint32_t)C::kMetaDepth;
+            uint32_t it = 0, gph = 0, nd = 0;              // stage it = gs + n * kStages, nd = n % D
+            bool issued = false, stop = false;
+            // The loop over the ring slots is unrolled, so that the slot's barrier addresses and
+            // operand descriptors are constants of the code: this thread's instruction count per
+            // stage is what bounds the kernel once the gathers keep up.
+            while (!stop) {
 #pragma unroll
-                for (int m = 0; m < MMAS_PER_STAGE; ++m) {
-                    if (m < nmma && alive && (kstep_flags(cmd, m) & KS_FIRST)) {
+                for (int gs = 0; gs < C::kStages; ++gs) {
+                    // The producers arrive on full_g only after they have seen full_m of the same stage,
+                    // so this one wait also covers the tile values and the command word.
+                    if (!mbar_wait_t<PROF>(smem_u32(&ss->full_g[gs]), gph, abort_flag, limit, w_fg, 1)) { raise(prm, ss, ST_TIMEOUT_FULL); stop = true; break; }
+                    prof_mark<PROF>(prm.dbg, it, 5);
+                    const uint32_t ms = (uint32_t)gs * D + nd;     // the stage's meta slot
+                    const uint32_t cmd = *reinterpret_cast<const volatile uint32_t *>(ring_m + ms * META_BYTES + META_TILE_BYTES + META_COL_BYTES);
+                    if (cmd & CMD_END) { stop = true; break; }
+                    if (cmd & CMD_FIRST) {
                         buf = ai % NACC;
                         const uint32_t aph = (ai / NACC) & 1u;
                         ++ai;
-                        if (!mbar_wait_t<PROF>(smem_u32(&ss->acc_empty[buf]), aph ^ 1u, abort_flag, w_acc)) { raise(prm, ss, ST_TIMEOUT_ACC); alive = false; }
+                        if (!mbar_wait_t<PROF>(smem_u32(&ss->acc_empty[buf]), aph ^ 1u, abort_flag, limit, w_acc)) { raise(prm, ss, ST_TIMEOUT_ACC); stop = true; break; }
+                        tc_fence_after();              // the epilogue's tcgen05.ld of this buffer happened before
                     }
-                    kbuf[m] = buf;
-                    dt[m] = tmem_base + buf * C::kAccCols;
-                }
-                if (!alive) break;
-                tc_fence_after();
+                    // (the copied data is handed over by the mbarrier its bytes complete on: no fence)
+                    const uint32_t d_tmem = tmem_base + buf * C::kAccCols;
+                    const uint64_t ad = a_desc0 + (uint64_t)(gs * (C::kStageBytes >> 4));
+                    const uint64_t bd = b_desc0 + (uint64_t)(ms * (META_BYTES >> 4));
+                    const uint32_t first = (cmd & CMD_FIRST) ? 0u : 1u;
+                    if (!(skip & SKIP_MMA)) {
+                        if ((cmd & CMD_COUNT) == (uint32_t)STAGE_TILES) {       // a full stage: no per-K-step tests
 #pragma unroll
-                for (int m = 0; m < MMAS_PER_STAGE; ++m) {
-                    if (m < nmma) {
-                        const uint32_t f = kstep_flags(cmd, m);
-                        if (!(prm.skip & 1)) {
+                            for (int m = 0; m < MMAS_PER_STAGE; ++m)
 #pragma unroll
-                            for (int h = 0; h < NH; ++h)
-                                umma_f16(dt[m] + h * 16, ad + (uint64_t)(((m * NH + h) * A_MMA_BYTES) >> 4),
-                                         bd + (uint64_t)((m * 2 * TILE_BYTES) >> 4), idesc, (f & KS_FIRST) ? 0u : 1u);
+                                for (int h = 0; h < NH; ++h) {
+                                    const uint64_t am = ad + (uint64_t)(((m * NH + h) * A_MMA_BYTES) >> 4), bm = bd + (uint64_t)((m * 2 * TILE_BYTES) >> 4);
+                                    if (m == 0) umma_f16(d_tmem + h * 16, am, bm, idesc, first);
+                                    else umma_f16_acc(d_tmem + h * 16, am, bm, idesc);
+                                }
+                        } else {
+                            const int nmma = (int)((cmd & CMD_COUNT) + 1u) >> 1;
+#pragma unroll
+                            for (int m = 0; m < MMAS_PER_STAGE; ++m)
+                                if (m < nmma) {
+#pragma unroll
+                                    for (int h = 0; h < NH; ++h)
+                                        umma_f16(d_tmem + h * 16, ad + (uint64_t)(((m * NH + h) * A_MMA_BYTES) >> 4),
+                                                 bd + (uint64_t)((m * 2 * TILE_BYTES) >> 4), idesc, m > 0 ? 1u : first);
+                                }
                         }
-                        if (f & KS_LAST) umma_commit(smem_u32(&ss->acc_full[kbuf[m]]));
                     }
+                    issued = true;
+                    umma_commit(smem_u32(&ss->empty_g[gs]));
+                    if (cmd & CMD_LAST) umma_commit(smem_u32(&ss->acc_full[buf]));
+                    prof_mark<PROF>(prm.dbg, it, 6);
+                    ++it;
                 }
-#else
-                const int nmma = (int)((cmd & CMD_COUNT) + 1u) >> 1;
-                if (cmd & CMD_FIRST) {
-                    buf = ai % NACC;
-                    const uint32_t aph = (ai / NACC) & 1u;
-                    ++ai;
-                    if (!mbar_wait_t<PROF>(smem_u32(&ss->acc_empty[buf]), aph ^ 1u, abort_flag, w_acc)) { raise(prm, ss, ST_TIMEOUT_ACC); break; }
-                }
-                // cp.async data is handed over by the mbarrier the producers arrive on after their
-                // copies have landed; no generic->async proxy fence is issued here (it would also
-                // wait for every younger gather in flight)
-                const long long tf0 = prof_clock<PROF>();
-                tc_fence_after();
-                const long long ti0 = prof_clock<PROF>();
-                t_fence += ti0 - tf0;
-                const uint32_t d_tmem = tmem_base + buf * C::kAccCols;
-                const uint64_t ad = a_desc0 + (uint64_t)(gs * (C::kStageBytes >> 4));
-                const uint64_t bd = b_desc0 + (uint64_t)(ms * (META_BYTES >> 4));
-                const uint32_t first = (cmd & CMD_FIRST) ? 0u : 1u;
-#pragma unroll
-                for (int m = 0; m < MMAS_PER_STAGE; ++m) {
-                    if (m < nmma && !(prm.skip & 1)) {
-#pragma unroll
-                        for (int h = 0; h < NH; ++h)
-                            umma_f16(d_tmem + h * 16, ad + (uint64_t)(((m * NH + h) * A_MMA_BYTES) >> 4),
-                                     bd + (uint64_t)((m * 2 * TILE_BYTES) >> 4), idesc, m > 0 ? 1u : first);
-                    }
-                }
-#endif
-                const long long ti1 = prof_clock<PROF>();
-                umma_commit(smem_u32(&ss->empty_g[gs]));
-#if !GRWS_TC5_SPAN
-                if (cmd & CMD_LAST) umma_commit(smem_u32(&ss->acc_full[buf]));
-#endif
-                const long long ti2 = prof_clock<PROF>();
-                t_issue += ti1 - ti0;
-                t_commit += ti2 - ti1;
-                prof_mark<PROF>(prm.dbg, it, 6);
-                if (++gs == (uint32_t)C::kStages) { gs = 0; gph ^= 1u; }
-                if (++ms == (uint32_t)C::kMeta) ms = 0;
+                gph ^= 1u;
+                if (++nd == D) nd = 0;
+            }
+            if (issued && *abort_flag) {
+                // aborted: tensor memory is freed below, so the MMAs still in the pipe must finish first
+                umma_commit(smem_u32(&ss->drain));
+                (void)mbar_wait_drain(smem_u32(&ss->drain), 0u, limit);
             }
             if (PROF && prm.dbg) {
                 long long *d = prm.dbg + blockIdx.x * 16;
-                d[4] = w_acc; d[5] = w_fm; d[6] = w_fg; d[8] = t_issue; d[9] = t_commit; d[10] = prof_clock<PROF>() - t_mark; d[11] = it; d[12] = t_cmd; d[13] = t_fence;
+                d[4] = w_acc; d[6] = w_fg; d[10] = prof_clock<PROF>() - t_mark; d[11] = it;
             }
         }
         __syncwarp();
@@ -888,39 +888,78 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
     }
 }
 
-static int grid_size() {
-    static const int sms = [] {
-        int dev = 0, n = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess) return 148;
-        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) return 148;
-        return n;
-    }();
-    return sms;
-}
-
+// ---------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------
 constexpr size_t STATUS_BYTES = 256;
-constexpr size_t DEBUG_BYTES = 1024 * 16 * sizeof(long long);
+constexpr size_t DEBUG_BYTES = 1024 * 16 * sizeof(long long);   // profiling counters (unused by the product kernel, kept in the layout)
 constexpr size_t FIX_BYTES = 1024 * 4 * sizeof(int64_t);      // per-CTA counters of finished pieces of split windows
+constexpr int SCRATCH_CTAS_PER_SM = 4;                        // partial-tile slots are sized for up to this many CTAs per SM
+static_assert(GRWS_TC5_CTAS_PER_SM <= SCRATCH_CTAS_PER_SM, "scratch sizing");
 
-static bool profile_waits() {
-    static const int v = [] { const char *e = getenv("GRWS_TC5_PROFILE"); return e ? atoi(e) : 0; }();
-    return v != 0;
+// Worst status any SpMM launch on this device has reported since the word was last cleared
+// (grws_spmm_last_status / grws_spmm_check read it): callers that never look at the status word
+// of their scratch buffer, or that use the built-in scratch, learn of a timed-out pipeline here.
+static __device__ int g_sticky_status;
+
+// What the host keeps per device: properties read once, the kernels' shared-memory opt-in, and the
+// device addresses of the library's __device__ variables (their names are host-side handles only).
+struct DeviceState {
+    int ready;                 // 0 = not set up, 1 = set up (release / acquire)
+    int sms;
+    int *sticky;               // device address of g_sticky_status
+    void *static_scratch;      // device address of the built-in scratch array (looked up on first use)
+};
+constexpr int MAX_DEVICES = 64;
+static DeviceState g_devices[MAX_DEVICES];
+static long long g_wait_limit = WAIT_LIMIT_CYCLES;
+
+template <int NH>
+static cudaError_t opt_in_smem() {
+    cudaError_t e = cudaFuncSetAttribute(spmm_tc5_kernel<NH, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<NH>::kSmem);
+#ifdef GRWS_TC5_PROFILING
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(spmm_tc5_kernel<NH, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<NH>::kSmem);
+#endif
+    return e;
 }
 
-}  // namespace tc5
+// state of the current device; the first call on a device sets it up (with that device current)
+static int device_state(DeviceState **out) {
+    int dev = 0;
+    GRWS_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= MAX_DEVICES) return fail(GRWS_ERR_UNSUPPORTED, "device ordinal %d beyond %d", dev, MAX_DEVICES);
+    DeviceState *d = &g_devices[dev];
+    if (!__atomic_load_n(&d->ready, __ATOMIC_ACQUIRE)) {
+        // two threads may both get here: they compute the same values, the stores are idempotent
+        int sms = 0;
+        GRWS_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+        if (sms <= 0) return fail(GRWS_ERR_CUDA, "device %d reports %d SMs", dev, sms);
+        GRWS_CUDA_TRY(opt_in_smem<1>());
+        GRWS_CUDA_TRY(opt_in_smem<2>());
+        void *p = nullptr;
+        GRWS_CUDA_TRY(cudaGetSymbolAddress(&p, g_sticky_status));
+        if (p == nullptr) return fail(GRWS_ERR_CUDA, "cudaGetSymbolAddress returned a null address");
+        d->sms = sms;
+        d->sticky = static_cast<int *>(p);
+        __atomic_store_n(&d->ready, 1, __ATOMIC_RELEASE);
+    }
+    *out = d;
+    return GRWS_OK;
+}
 
-namespace tc5 {
+#ifdef GRWS_TC5_PROFILING
+static int profile_env(const char *name) {
+    const char *e = getenv(name);
+    return e ? atoi(e) : 0;
+}
+#endif
+
 template <int NH>
-static cudaError_t launch_kernel(const Params &prm, const CUtensorMap &b_map, int G, cudaStream_t stream) {
-    static const cudaError_t attr = [] {
-        cudaError_t e = cudaFuncSetAttribute(spmm_tc5_kernel<NH, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<NH>::kSmem);
-        if (e != cudaSuccess) return e;
-        return cudaFuncSetAttribute(spmm_tc5_kernel<NH, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<NH>::kSmem);
-    }();
-    if (attr != cudaSuccess) return attr;
-    if (prm.dbg) spmm_tc5_kernel<NH, true><<<G, NUM_THREADS, Cfg<NH>::kSmem, stream>>>(prm, b_map);
-    else spmm_tc5_kernel<NH, false><<<G, NUM_THREADS, Cfg<NH>::kSmem, stream>>>(prm, b_map);
-    return cudaSuccess;
+static void launch_kernel(const Params &prm, const CUtensorMap &b_map, int G, cudaStream_t stream) {
+#ifdef GRWS_TC5_PROFILING
+    if (prm.dbg) { spmm_tc5_kernel<NH, true><<<G, NUM_THREADS, Cfg<NH>::kSmem, stream>>>(prm, b_map); return; }
+#endif
+    spmm_tc5_kernel<NH, false><<<G, NUM_THREADS, Cfg<NH>::kSmem, stream>>>(prm, b_map);
 }
 
 // Tensor map of the dense operand for the row gathers: 2-D [K rows][N features], box of one row
@@ -938,7 +977,7 @@ static int encode_b_map(CUtensorMap *map, const void *B, int is_bf16, int64_t K,
         return reinterpret_cast<EncodeFn>(fn);
     }();
     if (!encode) return fail(GRWS_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
-    const cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)(K > 0 ? K : 1)};
+    const cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)K};
     const cuuint64_t strides[1] = {(cuuint64_t)ldb * 2};
     const cuuint32_t box[2] = {64, 1};
     const cuuint32_t estr[2] = {1, 1};
@@ -952,13 +991,36 @@ static int encode_b_map(CUtensorMap *map, const void *B, int is_bf16, int64_t K,
 }  // namespace tc5
 
 bool spmm_tc5_supported(int dtype, int64_t N) {
-    static const int disabled = [] { const char *e = getenv("GRWS_DISABLE_TCGEN05"); return e ? atoi(e) : 0; }();
-    return !disabled && (dtype == GRWS_F16 || dtype == GRWS_BF16) && (N == 128 || N == 256);
+    return (dtype == GRWS_F16 || dtype == GRWS_BF16) && (N == 128 || N == 256);
 }
 
+// Scratch of one call: status word | split-window counters | profiling counters | two fp32 partial
+// tiles per CTA.  0 when the device cannot be queried (the launch then reports the error).
 size_t spmm_tc5_scratch_bytes(int64_t num_tiles_bound, int64_t N) {
     (void)num_tiles_bound;
-    return tc5::STATUS_BYTES + tc5::DEBUG_BYTES + tc5::FIX_BYTES + (size_t)tc5::grid_size() * 4 /* CTAs per SM, at most */ * 2 * TILE_ROWS * (size_t)N * sizeof(float);
+    tc5::DeviceState *d = nullptr;
+    if (tc5::device_state(&d) != GRWS_OK) return 0;
+    return tc5::STATUS_BYTES + tc5::DEBUG_BYTES + tc5::FIX_BYTES +
+           (size_t)d->sms * tc5::SCRATCH_CTAS_PER_SM * 2 * TILE_ROWS * (size_t)N * sizeof(float);
+}
+
+__global__ void spmm_zero_rows_kernel(void *C, int64_t rows, int64_t row_bytes16, int64_t ld_bytes16) {
+    // 16-byte pieces of `rows` rows of C (rows are 16-byte aligned)
+    const int64_t n = rows * row_bytes16;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+        reinterpret_cast<uint4 *>(C)[(i / row_bytes16) * ld_bytes16 + i % row_bytes16] = make_uint4(0u, 0u, 0u, 0u);
+}
+
+// C = 0 for a product without tiles or without dense rows (the kernels never run on it)
+int spmm_zero_output(void *C, int c_dtype, int64_t ldc, int64_t W, int64_t N, cudaStream_t stream) {
+    const int64_t rows = W * TILE_ROWS, esz = (int64_t)dtype_bytes(c_dtype);
+    if (rows == 0) return GRWS_OK;
+    const int64_t pieces = rows * (N * esz / 16);
+    int64_t blocks = ceil_div(pieces, 256);
+    if (blocks > 4096) blocks = 4096;
+    spmm_zero_rows_kernel<<<(unsigned)blocks, 256, 0, stream>>>(C, rows, N * esz / 16, ldc * esz / 16);
+    GRWS_CUDA_TRY(cudaGetLastError());
+    return GRWS_OK;
 }
 
 int spmm_tc5_launch(const int64_t *window_offset, const int32_t *cols, const void *vals, int dtype,
@@ -966,16 +1028,27 @@ int spmm_tc5_launch(const int64_t *window_offset, const int32_t *cols, const voi
                     int64_t num_tiles_bound, int64_t K, int64_t N, void *scratch, size_t scratch_bytes,
                     cudaStream_t stream) {
     using namespace tc5;
+    DeviceState *dev = nullptr;
+    if (int st = device_state(&dev)) return st;
     const size_t need = spmm_tc5_scratch_bytes(num_tiles_bound, N);
     if (scratch_bytes < need || scratch == nullptr)
         return fail(GRWS_ERR_SCRATCH, "spmm scratch too small: %zu < %zu bytes", scratch_bytes, need);
     Params prm;
     prm.window_offset = window_offset; prm.cols = cols; prm.vals = vals; prm.B = B; prm.C = C;
     prm.status = static_cast<int *>(scratch);
-    { static const int sk = [] { const char *e = getenv("GRWS_TC5_SKIP"); return e ? atoi(e) : 0; }(); prm.skip = sk; }
-    { static const int lw = [] { const char *e = getenv("GRWS_TC5_LW_SHIFT"); return e ? atoi(e) : 4; }(); prm.lw_shift = lw; }
+    prm.sticky = dev->sticky;
+    prm.skip = 0;
+    prm.dbg = nullptr;
+    prm.wait_limit = __atomic_load_n(&g_wait_limit, __ATOMIC_RELAXED);
+#ifdef GRWS_TC5_PROFILING
+    // profiling build only: GRWS_TC5_PROFILE=1 records wait times and a stage timeline behind the
+    // split-window counters, GRWS_TC5_SKIP leaves parts of the work out (see the SKIP_* bits)
+    if (profile_env("GRWS_TC5_PROFILE")) {
+        prm.dbg = reinterpret_cast<long long *>(static_cast<char *>(scratch) + STATUS_BYTES + FIX_BYTES);
+        prm.skip = profile_env("GRWS_TC5_SKIP");
+    }
+#endif
     // layout: status word | split-window counters | profiling counters | partial tiles; the first two are zeroed together
-    prm.dbg = profile_waits() ? reinterpret_cast<long long *>(static_cast<char *>(scratch) + STATUS_BYTES + FIX_BYTES) : nullptr;
     prm.split_count = reinterpret_cast<int *>(static_cast<char *>(scratch) + STATUS_BYTES);
     prm.partial = reinterpret_cast<float *>(static_cast<char *>(scratch) + STATUS_BYTES + DEBUG_BYTES + FIX_BYTES);
     prm.W = W; prm.N = N; prm.ldb = ldb; prm.ldc = ldc; prm.c_dtype = c_dtype;
@@ -984,11 +1057,11 @@ int spmm_tc5_launch(const int64_t *window_offset, const int32_t *cols, const voi
     // Two passes read the tiles twice but gather from half as many bytes of the dense operand,
     // which then stays in L2 next to the tile stream, and they run two CTAs per SM: measured 4 %
     // faster at 86 MB of operand, 20 % at 119 MB.  Small operands keep the single pass (half the
-    // launches).  GRWS_TC5_SPLIT256 = 0 / 1 forces one way.
-    static const int split_env = [] { const char *e = getenv("GRWS_TC5_SPLIT256"); return e ? atoi(e) : -1; }();
-    const bool split = N == 256 && (split_env >= 0 ? split_env != 0 : K * 512 > SPLIT256_OPERAND_BYTES);
+    // launches).
+    const bool split = N == 256 && K * 512 > SPLIT256_OPERAND_BYTES;
     const int64_t pass_n = (N == 128 || split) ? 128 : 256;
-    const int G = grid_size() * (pass_n == 128 ? Cfg<1>::kCtasPerSm : Cfg<2>::kCtasPerSm);
+    const int G = dev->sms * (pass_n == 128 ? Cfg<1>::kCtasPerSm : Cfg<2>::kCtasPerSm);
+    if ((size_t)G * sizeof(int) > FIX_BYTES) return fail(GRWS_ERR_UNSUPPORTED, "more CTAs (%d) than split-window counters", G);
     const size_t c_elem = c_dtype == GRWS_F32 ? 4 : 2;
     for (int64_t col0 = 0; col0 < N; col0 += pass_n) {
         prm.B = static_cast<const char *>(B) + col0 * 2;
@@ -999,18 +1072,54 @@ int spmm_tc5_launch(const int64_t *window_offset, const int32_t *cols, const voi
         // the status word is cleared once per call, the split-window counters before every pass
         if (col0 == 0) GRWS_CUDA_TRY(cudaMemsetAsync(scratch, 0, STATUS_BYTES + sizeof(int) * (size_t)G, stream));
         else GRWS_CUDA_TRY(cudaMemsetAsync(prm.split_count, 0, sizeof(int) * (size_t)G, stream));
-        GRWS_CUDA_TRY((pass_n == 128 ? launch_kernel<1>(prm, b_map, G, stream) : launch_kernel<2>(prm, b_map, G, stream)));
+        if (pass_n == 128) launch_kernel<1>(prm, b_map, G, stream);
+        else launch_kernel<2>(prm, b_map, G, stream);
         GRWS_CUDA_TRY(cudaGetLastError());
-    }
-    if (prm.dbg) {      // profiling build: failed try_waits per role since the last call, behind the timeline
-        GRWS_CUDA_TRY(cudaMemcpyFromSymbolAsync(prm.dbg + 12288 + 64 * 8, g_prof_tries, sizeof(g_prof_tries), 0, cudaMemcpyDeviceToDevice, stream));
-        static const unsigned long long zeros[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        GRWS_CUDA_TRY(cudaMemcpyToSymbolAsync(g_prof_tries, zeros, sizeof(zeros), 0, cudaMemcpyHostToDevice, stream));
     }
     return GRWS_OK;
 }
 
 }  // namespace grws
+
+// ---------------------------------------------------------------------------------------------
+// Status of the tcgen05 SpMM launches of the current device.
+// ---------------------------------------------------------------------------------------------
+extern "C" __attribute__((visibility("default")))
+int grws_spmm_last_status(int *out_status, int reset, void *stream) {
+    using namespace grws;
+    GRWS_REQUIRE(out_status != nullptr, "null pointer");
+    tc5::DeviceState *d = nullptr;
+    if (int st = tc5::device_state(&d)) return st;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    GRWS_CUDA_TRY(cudaMemcpyAsync(out_status, d->sticky, sizeof(int), cudaMemcpyDefault, s));
+    if (reset) GRWS_CUDA_TRY(cudaMemsetAsync(d->sticky, 0, sizeof(int), s));
+    return GRWS_OK;
+}
+
+extern "C" __attribute__((visibility("default")))
+int grws_spmm_check(void *stream) {
+    using namespace grws;
+    tc5::DeviceState *d = nullptr;
+    if (int st = tc5::device_state(&d)) return st;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    int status = 0;
+    GRWS_CUDA_TRY(cudaMemcpyAsync(&status, d->sticky, sizeof(int), cudaMemcpyDeviceToHost, s));
+    GRWS_CUDA_TRY(cudaStreamSynchronize(s));
+    if (status == 0) return GRWS_OK;
+    GRWS_CUDA_TRY(cudaMemsetAsync(d->sticky, 0, sizeof(int), s));
+    static const char *const what[] = {"", "gathered rows never arrived (full_g)", "a gather slot was never released (empty_g)",
+                                       "an accumulator hand-over never happened (acc)", "tiles / column ids never arrived (meta)"};
+    return fail(GRWS_ERR_DEVICE, "a tcgen05 SpMM launch on this device gave up waiting: %s (code %d); its output is incomplete",
+                status >= 1 && status <= 4 ? what[status] : "unknown wait", status);
+}
+
+extern "C" __attribute__((visibility("default")))
+int grws_spmm_set_wait_limit(long long sm_clocks) {
+    using namespace grws;
+    GRWS_REQUIRE(sm_clocks >= 0, "negative limit");
+    __atomic_store_n(&tc5::g_wait_limit, sm_clocks > 0 ? sm_clocks : tc5::WAIT_LIMIT_CYCLES, __ATOMIC_RELAXED);
+    return GRWS_OK;
+}
 
 // ---------------------------------------------------------------------------------------------
 // Forward SpMM for callers that must not allocate device memory.
@@ -1032,6 +1141,8 @@ int spmm_tc5_launch(const int64_t *window_offset, const int32_t *cols, const voi
 //     on the stream before each launch, everything else is written before it is read within a
 //     call.  Two calls that overlap on the GPU (different streams, or one device used from two
 //     threads) race on it; serialise them or use grws_spmm_fwd with separate scratch buffers.
+//   * The call's status word lives inside the array, out of the caller's reach: a pipeline wait
+//     that ran out is reported through grws_spmm_last_status / grws_spmm_check instead.
 //   * No cudaMalloc, cudaFree or allocating library routine is called.
 // ---------------------------------------------------------------------------------------------
 namespace grws {
@@ -1040,23 +1151,20 @@ namespace tc5 {
 constexpr int STATIC_MAX_SMS = 160;
 constexpr int STATIC_MAX_N = 256;
 constexpr size_t STATIC_SCRATCH_BYTES =
-    STATUS_BYTES + DEBUG_BYTES + FIX_BYTES + (size_t)STATIC_MAX_SMS * 4 * 2 * TILE_ROWS * STATIC_MAX_N * sizeof(float);
+    STATUS_BYTES + DEBUG_BYTES + FIX_BYTES + (size_t)STATIC_MAX_SMS * SCRATCH_CTAS_PER_SM * 2 * TILE_ROWS * STATIC_MAX_N * sizeof(float);
 static_assert(STATIC_SCRATCH_BYTES == GRWS_SPMM_STATIC_SCRATCH_BYTES, "the header states the size of the built-in scratch");
 
 static __device__ __align__(256) unsigned char static_scratch[STATIC_SCRATCH_BYTES];
 
 // device address of static_scratch on the current device (looked up once per device)
 static int static_scratch_address(void **out) {
-    constexpr int MAX_DEVICES = 64;
-    static void *cached[MAX_DEVICES] = {nullptr};
-    int dev = 0;
-    GRWS_CUDA_TRY(cudaGetDevice(&dev));
-    if (dev < 0 || dev >= MAX_DEVICES) return fail(GRWS_ERR_UNSUPPORTED, "device ordinal %d beyond %d", dev, MAX_DEVICES);
-    void *p = __atomic_load_n(&cached[dev], __ATOMIC_ACQUIRE);
+    DeviceState *d = nullptr;
+    if (int st = device_state(&d)) return st;
+    void *p = __atomic_load_n(&d->static_scratch, __ATOMIC_ACQUIRE);
     if (p == nullptr) {
         GRWS_CUDA_TRY(cudaGetSymbolAddress(&p, static_scratch));
         if (p == nullptr) return fail(GRWS_ERR_CUDA, "cudaGetSymbolAddress returned a null address");
-        __atomic_store_n(&cached[dev], p, __ATOMIC_RELEASE);      // every thread resolves the same address
+        __atomic_store_n(&d->static_scratch, p, __ATOMIC_RELEASE);      // every thread resolves the same address
     }
     *out = p;
     return GRWS_OK;
@@ -1072,7 +1180,7 @@ int grws_spmm_fwd_static(const int64_t *window_offset, const int32_t *cols, cons
     using namespace grws;
     GRWS_REQUIRE(num_windows >= 0 && num_tiles_bound >= 0 && K >= 0 && N > 0, "negative size");
     if (num_windows == 0) return GRWS_OK;
-    GRWS_REQUIRE(window_offset && C && (num_tiles_bound == 0 || (cols && vals && B)), "null pointer");
+    GRWS_REQUIRE(window_offset && C && (num_tiles_bound == 0 || K == 0 || (cols && vals && B)), "null pointer");
     GRWS_REQUIRE(c_dtype >= GRWS_F32 && c_dtype <= GRWS_BF16, "bad output dtype %d", c_dtype);
     if (val_dtype != b_dtype || !(val_dtype == GRWS_F16 || val_dtype == GRWS_BF16) || !(N == 128 || N == 256))
         return fail(GRWS_ERR_UNSUPPORTED,
@@ -1081,7 +1189,10 @@ int grws_spmm_fwd_static(const int64_t *window_offset, const int32_t *cols, cons
     GRWS_REQUIRE(ldb >= N && ldc >= N, "leading dimension smaller than N");
     GRWS_REQUIRE((ldb * 2) % 16 == 0 && (ldc * dtype_bytes(c_dtype)) % 16 == 0, "rows of B and C must be 16-byte aligned");
     GRWS_REQUIRE(aligned16(B) && aligned16(C) && aligned16(vals) && aligned16(cols), "B, C, values and column ids must be 16-byte aligned");
+    if (num_tiles_bound == 0 || K == 0)      // nothing to multiply: the rows are zeros
+        return spmm_zero_output(C, c_dtype, ldc, num_windows, N, static_cast<cudaStream_t>(stream));
     const size_t need = spmm_tc5_scratch_bytes(num_tiles_bound, N);
+    if (need == 0) return GRWS_ERR_CUDA;
     if (need > tc5::STATIC_SCRATCH_BYTES)
         return fail(GRWS_ERR_SCRATCH, "this device needs %zu bytes of SpMM scratch, the built-in array holds %zu "
                     "(more than %d SMs?); use grws_spmm_fwd with caller scratch", need, tc5::STATIC_SCRATCH_BYTES, tc5::STATIC_MAX_SMS);

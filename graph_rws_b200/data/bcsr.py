@@ -91,9 +91,12 @@ class BCSRGraph:
         hit = self._shared.get(key)
         if hit is not None and hit[0] == self._versions():
             return hit[1]
+        # a block that lives for one step skips the size read-backs: its tile arrays are sized by
+        # a bound, and so is its entry count when the sampler recorded one (``nnz_bound``)
         wo, cols, vals = bcsr_transpose(self.window_offset, self.original_col_indices,
                                         self.values_condensed, n, values_dtype=dtype,
-                                        exact=not getattr(self, 'transient', False))
+                                        exact=not getattr(self, 'transient', False),
+                                        nnz_bound=getattr(self, 'nnz_bound', None))
         gt = BCSRGraph(num_nodes=n, num_edges=None, tile_rows=self.tile_rows, tile_cols=self.tile_cols,
                        window_offset=wo, original_col_indices=cols, values_condensed=vals,
                        device=vals.device, num_rows=n, num_cols=self.num_windows * self.tile_rows,

@@ -159,6 +159,57 @@ def community_csr_torch(n: int, e_target: int, num_comm: int, intra: float, seed
     return rp, c.int(), val
 
 
+def chung_lu_csr_torch(n: int, e_target: int, gamma: float, seed: int, device):
+    """``chung_lu_edges`` + ``sym_normalized_csr`` with torch ops on ``device``: the power-law graph
+    of the sampled-training configurations at full size (2.45 M nodes, 61.86 M undirected edges)
+    takes seconds on a GPU, minutes with numpy.  Same distribution, another random stream; every
+    device of one type draws the same graph from the same seed.  Returns
+    (row_ptr int64 [n+1], col_idx int32 [nnz], values float32 [nnz]) on ``device``."""
+    import torch
+    gen = torch.Generator(device=device).manual_seed(seed)
+    w = (torch.arange(n, dtype=torch.float64, device=device) + 1.0) ** (-1.0 / (gamma - 1.0))
+    cdf = torch.cumsum(w, 0)
+    cdf /= cdf[-1].clone()
+    del w
+    perm = torch.randperm(n, generator=gen, device=device)
+    got = torch.empty(0, dtype=torch.int64, device=device)
+    while got.numel() < e_target:
+        m = int((e_target - got.numel()) * 1.3) + 4096
+        u = perm[torch.searchsorted(cdf, torch.rand(m, generator=gen, device=device, dtype=torch.float64)).clamp_(max=n - 1)]
+        v = perm[torch.searchsorted(cdf, torch.rand(m, generator=gen, device=device, dtype=torch.float64)).clamp_(max=n - 1)]
+        keep = u != v
+        u, v = u[keep], v[keep]
+        got = torch.unique(torch.cat([got, torch.minimum(u, v) * n + torch.maximum(u, v)]))
+        del u, v, keep
+        if got.numel() > e_target:
+            got = got[torch.randperm(got.numel(), generator=gen, device=device)[:e_target]]
+    del cdf, perm
+    u, v = got // n, got % n
+    loops = torch.arange(n, dtype=torch.int64, device=device)
+    key = torch.unique(torch.cat([u * n + v, v * n + u, loops * n + loops]))
+    del got, u, v, loops
+    r, c = key // n, key % n
+    del key
+    counts = torch.bincount(r, minlength=n)
+    dinv = counts.clamp(min=1).double() ** -0.5
+    val = (dinv[r] * dinv[c]).float()
+    rp = torch.zeros(n + 1, dtype=torch.int64, device=device)
+    torch.cumsum(counts, 0, out=rp[1:])
+    return rp, c.int(), val
+
+
+def sampling_algorithmic_bytes(frontier_sizes, sampled_edges, block_tiles, block_windows, val_bytes: int = 4) -> dict:
+    """Compulsory traffic of the sampling side of one mini-batch step, per hop h with frontier F_h,
+    sampled edges S_h and a block of T_h tiles in W_h windows.  Sampling: two int64 row offsets per
+    frontier node, one column id read and one neighbour id + weight written per sampled edge
+    (16 F + 4 S + 8 S).  Dedup / reindex / block build: every sampled id read and its local id
+    written (8 S), then the block (32 + 128 * sizeof(value) bytes per tile, 8 bytes per window)."""
+    sample = sum(16 * f + 12 * s for f, s in zip(frontier_sizes, sampled_edges))
+    build = sum(8 * s + t * (32 + 128 * val_bytes) + 8 * (w + 1)
+                for s, t, w in zip(sampled_edges, block_tiles, block_windows))
+    return {"sample": int(sample), "build": int(build), "total": int(sample + build)}
+
+
 def spmm_algorithmic_bytes(num_windows: int, num_tiles: int, k_touched: int, n: int,
                            val_bytes: int, b_bytes: int, c_bytes: int) -> int:
     """Compulsory traffic of one BCSR SpMM: offsets + column ids + tile values + every touched

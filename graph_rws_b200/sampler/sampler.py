@@ -20,7 +20,7 @@ from typing import List
 import torch
 
 from .. import core
-from ..data import BCSRGraph
+from ..data import BCSRGraph, CSRTopology
 
 
 class BCSRSampler:
@@ -42,7 +42,8 @@ class BCSRSampler:
                  score_scale: float = 100.0,
                  locality_enabled: bool = False,
                  seed: int = core.sampling.DEFAULT_SEED,
-                 pad_to: int = 0):
+                 pad_to: int = 0,
+                 fused: bool = None):
         if hacs_enabled or locality_enabled:
             raise ValueError("importance-score sampling is not part of this library; sampling is uniform")
         if tile_rows != 16 or tile_cols != 8:
@@ -59,6 +60,11 @@ class BCSRSampler:
         # dense products of a training step see recurring shapes (input_nodes then contains -1s)
         self.pad_to = int(pad_to)
         self.step = 0          # callers may bump this to decorrelate epochs: the stream key is seed + step
+        # fused: all hops in one library call, buffers sized by bounds, no size read-back (the
+        # blocks then have the sizes of core.sample_layers_sizes, their unused tails hold -1
+        # nodes).  Default: fused unless per-phase timings are wanted (``verbose``), which need
+        # a host synchronisation per phase anyway.
+        self.fused = (not verbose) if fused is None else bool(fused)
 
     @staticmethod
     def _to_cuda_int(x, device=None) -> torch.Tensor:
@@ -80,16 +86,32 @@ class BCSRSampler:
         g._shared['csr'] = (state, csr)
         return csr
 
-    def sample_layers(self, g: BCSRGraph, seed_nodes: torch.Tensor) -> List[BCSRGraph]:
-        device = g.window_offset.device if g.window_offset.is_cuda else torch.device('cuda')
+    def sample_layers(self, g, seed_nodes: torch.Tensor, seed_dev: torch.Tensor = None) -> List[BCSRGraph]:
+        """``g`` is the full graph: a ``BCSRGraph`` (its CSR view is extracted once and cached) or a
+        ``CSRTopology`` (no BCSR of the whole graph is ever built).  ``seed_dev``: optional device
+        uint64 tensor holding the Philox seed (fused path only), for step loops that replay one
+        captured launch sequence with a new seed each time."""
+        if isinstance(g, CSRTopology):
+            device = g.device
+            row_ptr, col_idx, values = g.csr()
+            block_dtype = g.block_dtype
+        else:
+            device = g.window_offset.device if g.window_offset.is_cuda else torch.device('cuda')
+            row_ptr, col_idx, values = self.graph_csr(g)
+            block_dtype = g.values_condensed.dtype
         seed_nodes = self._to_cuda_int(seed_nodes, device=device)
-        row_ptr, col_idx, values = self.graph_csr(g)
         # model layers run input -> output, sampling runs from the seeds outwards (sampler.py:200-204)
         reversed_fanouts = list(reversed(self.fanouts))
-        hops, timing_list = core.sample_layers_csr(row_ptr, col_idx, values, seed_nodes, reversed_fanouts,
-                                                   seed=self.seed + self.step,
-                                                   values_dtype=g.values_condensed.dtype, timing=self.verbose,
-                                                   pad_to=self.pad_to, exact=False)
+        if self.fused:
+            hops = core.sample_layers_fused(row_ptr, col_idx, values, seed_nodes, reversed_fanouts,
+                                            seed=self.seed + self.step, values_dtype=block_dtype,
+                                            pad_to=self.pad_to, seed_dev=seed_dev)
+            timing_list = []
+        else:
+            hops, timing_list = core.sample_layers_csr(row_ptr, col_idx, values, seed_nodes, reversed_fanouts,
+                                                       seed=self.seed + self.step,
+                                                       values_dtype=block_dtype, timing=self.verbose,
+                                                       pad_to=self.pad_to, exact=False)
         if self.verbose:
             num_layers = len(self.fanouts)
             for i, t in enumerate(timing_list):
@@ -101,9 +123,10 @@ class BCSRSampler:
                 stats['p3_recomp'] += t.phase3_recompression_time
                 stats['total'] += t.total_time
         layers: List[BCSRGraph] = []
-        for wo, cols, vals, dst, src in hops:
+        for (wo, cols, vals, dst, src), fanout in zip(hops, reversed_fanouts):
             sub = BCSRGraph.from_components(wo, cols, vals, num_rows=dst.numel(), num_cols=src.numel(),
                                             tile_rows=self.tile_rows, tile_cols=self.tile_cols, device=wo.device)
+            sub.nnz_bound = dst.numel() * fanout   # lets the transposed block be built without a read-back
             sub.output_nodes = dst          # global ids of the block's rows
             sub.input_nodes = src           # global ids of the block's columns; starts with output_nodes
             sub.transient = True            # lives for one step: its arrays and its transposed graph skip exact sizing

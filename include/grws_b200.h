@@ -81,6 +81,29 @@ int grws_spmm_fwd(const int64_t *window_offset, const int32_t *cols, const void 
                   void *scratch, size_t scratch_bytes, int algo, void *stream);
 
 /* ------------------------------------------------------------------------------------------
+ * Status of the tcgen05 SpMM launches.  The reference has no counterpart: its kernels cannot
+ * report anything (errors are host-side TORCH_CHECKs, core/wrapper/spmm_wrapper.cu:48-51).
+ * Every wait of the tcgen05 kernel on a shared-memory barrier is bounded; a launch whose wait
+ * runs out stops its pipeline, leaves its output incomplete, writes the code of the wait into
+ * the status word at the start of its scratch and into one word per device that keeps the worst
+ * code since it was last cleared.  Launches never synchronise, so the status is read separately:
+ *   grws_spmm_last_status : queues, on `stream`, a copy of the current device's word to
+ *                           `out_status` (device or pinned host memory) and, if `reset`, clears
+ *                           the word after the copy; no synchronisation;
+ *   grws_spmm_check       : synchronises `stream`, reads the word, clears it when non-zero and
+ *                           returns GRWS_ERR_DEVICE with a message naming the wait, else GRWS_OK.
+ *                           Call it where the host synchronises anyway (end of an epoch);
+ *   grws_spmm_set_wait_limit : the limit of one wait in SM clocks for launches made after the
+ *                           call (0 restores the default of 3e9, about 1.5 s); a diagnostic
+ *                           knob, process-wide.
+ * The first SpMM call or status call on a device looks up the word's device address
+ * (cudaGetSymbolAddress): make it before any stream capture.
+ * ------------------------------------------------------------------------------------------ */
+int grws_spmm_last_status(int *out_status, int reset, void *stream);
+int grws_spmm_check(void *stream);
+int grws_spmm_set_wait_limit(long long sm_clocks);
+
+/* ------------------------------------------------------------------------------------------
  * Forward SpMM that allocates nothing and takes no scratch buffer.  It has no counterpart in
  * the reference.  It exists for callers that cannot provide device scratch: code that runs
  * inside another framework's memory pool and only receives its input and output buffers, a
@@ -96,7 +119,9 @@ int grws_spmm_fwd(const int64_t *window_offset, const int32_t *cols, const void 
  *     make that first call before any stream capture;
  *   - every call shares the array, which keeps the previous call's contents (the status word is
  *     cleared on the stream before each launch).  Calls that overlap on the GPU race on it:
- *     issue them on one stream, or otherwise order them.
+ *     issue them on one stream, or otherwise order them;
+ *   - the status word of a call lives inside the array, out of the caller's reach: a wait that ran
+ *     out is reported through grws_spmm_last_status / grws_spmm_check.
  * Arguments as grws_spmm_fwd, without scratch and algo.
  * ------------------------------------------------------------------------------------------ */
 #define GRWS_SPMM_STATIC_SCRATCH_BYTES (256 + 131072 + 32768 + 160 * 4 * 2 * 16 * 256 * 4)
@@ -128,6 +153,22 @@ int grws_csr_to_bcsr_count(int64_t num_rows, const int64_t *row_ptr, const int32
 int grws_csr_to_bcsr_fill(int64_t num_rows, int64_t nnz, const int64_t *window_offset,
                           int64_t num_tiles, int32_t *out_cols, void *out_vals, int val_dtype,
                           void *scratch, size_t scratch_bytes, void *stream);
+
+/* The count phase for CSR arrays whose entry count the host knows only as a bound (per-step
+ * builders that must not read a size back): only the first row_ptr[num_rows] entries of col_idx
+ * and values exist, nnz_bound >= that count sizes the scratch (grws_csr_to_bcsr_scratch_bytes(
+ * num_rows, nnz_bound)) and is what grws_csr_to_bcsr_fill must be given as nnz. */
+int grws_csr_to_bcsr_count_bounded(int64_t num_rows, const int64_t *row_ptr, const int32_t *col_idx,
+                                   const float *values, int64_t nnz_bound, int64_t *window_offset,
+                                   void *scratch, size_t scratch_bytes, void *stream);
+
+/* The count phase straight from a hop's fixed-stride neighbour lists (this, with
+ * grws_csr_to_bcsr_fill, replaces build_col_to_val_map_kernel + recompress_sampled_bcsr_kernel,
+ * core/include/sampling.cuh:471-579,707-773): row i has the entries local[i*fanout + j] >= 0
+ * with weights w[i*fanout + j]; -1 marks an empty slot.  Scratch as
+ * grws_csr_to_bcsr_scratch_bytes(n_dst, n_dst*fanout); the fill call takes nnz = n_dst*fanout. */
+int grws_block_build_count(const int32_t *local, const float *w, int64_t n_dst, int fanout,
+                           int64_t *window_offset, void *scratch, size_t scratch_bytes, void *stream);
 
 /* ------------------------------------------------------------------------------------------
  * BCSR -> CSR of the transposed matrix (rows = the BCSR's column ids), the first half of
@@ -205,6 +246,40 @@ int grws_dedup_reindex(const int32_t *dst, int64_t n_dst, const int32_t *nbr, in
  * recompress_sampled_bcsr_kernel, core/include/sampling.cuh:471-579,707-773). */
 int grws_block_compact(const int32_t *local, const float *w, int64_t n_dst, int fanout,
                        const int64_t *row_ptr, int32_t *out_col, float *out_val, void *stream);
+
+/* ------------------------------------------------------------------------------------------
+ * All hops of a mini-batch in one call: the hop loop of bcsr_sample_all_layers_wrapper
+ * (core/wrapper/sampling_wrapper.cu:365-438) without its per-layer host synchronisation
+ * (sampling_wrapper.cu:339-344).  Per hop h (fanouts are consumed in the order given): sample the
+ * frontier as grws_sample_hop does, build the source list as grws_dedup_reindex does, build the
+ * hop's BCSR block from the lists.  Every buffer is sized by a bound the host computes from
+ * (num_seeds, fanouts, pad_to) alone -- grws_sample_layers_sizes -- so no size is read back:
+ *   n_dst[0] = num_seeds, n_src[h] = roundup(n_dst[h] * (1 + fanout[h]), pad_to),
+ *   n_dst[h+1] = n_src[h], tiles_bound[h] = n_dst[h]*fanout[h]/8 + ceil(n_dst[h]/16).
+ * The frontier of hop h+1 is the whole source list of hop h, padding entries (-1) included: they
+ * sample nothing and become rows without entries.  Outputs per hop h (arrays of num_hops host
+ * pointers to device memory):
+ *   out_src[h]           int32 [n_src[h]]   frontier ++ new nodes in ascending id order ++ -1
+ *   out_window_offset[h] int64 [ceil(n_dst[h]/16) + 1]
+ *   out_cols[h]          int32 [tiles_bound[h]*8], out_vals[h] [tiles_bound[h]*128] of val_dtype;
+ *                        tiles past window_offset's last entry are empty (-1 / 0)
+ *   out_counts           int64 [num_hops*4] or NULL: {source nodes incl. padded frontier entries,
+ *                        sampled edges, tiles, real frontier nodes} per hop, for reporting
+ * seed_dev, when not NULL, is a device uint64 read by the kernels instead of `seed` (a seed that
+ * changes between replays of a captured launch sequence).
+ * ------------------------------------------------------------------------------------------ */
+int grws_sample_layers_sizes(int64_t num_seeds, const int *fanouts, int num_hops, int64_t pad_to,
+                             int64_t *n_dst, int64_t *n_src, int64_t *tiles_bound);
+
+size_t grws_sample_layers_scratch_bytes(int64_t num_seeds, const int *fanouts, int num_hops,
+                                        int64_t pad_to);
+
+int grws_sample_layers(const int64_t *row_ptr, const int32_t *col_idx, const float *values,
+                       const int32_t *seeds, int64_t num_seeds, const int *fanouts, int num_hops,
+                       uint64_t seed, const uint64_t *seed_dev, int64_t pad_to, int val_dtype,
+                       int32_t *const *out_src, int64_t *const *out_window_offset,
+                       int32_t *const *out_cols, void *const *out_vals, int64_t *out_counts,
+                       void *scratch, size_t scratch_bytes, void *stream);
 
 /* ------------------------------------------------------------------------------------------
  * Global -> local column ids by window lookup, pruning misses.  Replaces reindex_bcsr_cuda +

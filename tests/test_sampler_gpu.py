@@ -82,7 +82,7 @@ def test_multi_hop_sampler_matches_replay(oracle, graph):
     assert np.array_equal(ci.cpu().numpy(), graph.col_idx)
     assert np.array_equal(vv.cpu().numpy(), graph.values)
     seeds = np.random.default_rng(1).permutation(graph.num_nodes)[:256].astype(np.int32)
-    sampler = BCSRSampler(fanouts=[15, 10, 5], verbose=False, seed=0x5EED)
+    sampler = BCSRSampler(fanouts=[15, 10, 5], verbose=False, seed=0x5EED, fused=False)      # exactly sized hops
     layers = sampler.sample_layers(g, torch.from_numpy(seeds))
     blocks = oracle.sample_layers(graph.row_ptr, graph.col_idx, graph.values, seeds, [15, 10, 5], 0x5EED)
     assert len(layers) == 3
@@ -132,8 +132,8 @@ def test_padded_hops_keep_the_real_part_identical(graph):
     from graph_rws_b200.sampler import BCSRSampler
     g = BCSRGraph.from_csr(graph.num_nodes, graph.row_ptr, graph.col_idx, graph.values, device=torch.device("cuda"))
     seeds = torch.arange(0, 600, 3, dtype=torch.int32)
-    exact = BCSRSampler([4, 3], verbose=False, seed=5).sample_layers(g, seeds)
-    padded = BCSRSampler([4, 3], verbose=False, seed=5, pad_to=512).sample_layers(g, seeds)
+    exact = BCSRSampler([4, 3], verbose=False, seed=5, fused=False).sample_layers(g, seeds)
+    padded = BCSRSampler([4, 3], verbose=False, seed=5, pad_to=512, fused=False).sample_layers(g, seeds)
     inner_e, inner_p = exact[1], padded[1]
     assert inner_p.num_cols % 512 == 0 and inner_p.num_cols >= inner_e.num_cols
     n = inner_e.num_cols
@@ -148,3 +148,62 @@ def test_padded_hops_keep_the_real_part_identical(graph):
     ce = outer_e.original_col_indices[:te * 8]
     shifted = torch.where(ce >= n, ce + (inner_p.num_cols - n), ce)
     assert torch.equal(outer_p.original_col_indices[:te * 8], shifted)
+
+
+@pytest.mark.parametrize("pad_to", [0, 512])
+def test_fused_all_hops_call_matches_replay(oracle, graph, pad_to):
+    """grws_sample_layers: every hop's source list, offsets, column ids and values equal the host
+    replay run on the same (padded) frontiers; buffers have the bound sizes and empty tails."""
+    from graph_rws_b200 import core
+    rp, ci, vv = _dev_csr(graph)
+    seeds = np.random.default_rng(11).permutation(graph.num_nodes)[:300].astype(np.int32)
+    fanouts = [5, 10, 15]                                  # in the order the hops consume them
+    n_dst, n_src, tiles = core.sample_layers_sizes(seeds.size, fanouts, pad_to)
+    assert n_dst[0] == seeds.size and all(n_dst[h + 1] == n_src[h] for h in range(2))
+    if pad_to:
+        assert all(n % pad_to == 0 for n in n_src)
+    hops, counts = core.sample_layers_fused(rp, ci, vv, torch.from_numpy(seeds), fanouts, seed=77, pad_to=pad_to,
+                                            want_counts=True)
+    torch.cuda.synchronize()
+    core.check_device_status()
+    counts = counts.cpu().numpy()
+    dst = seeds
+    for h, f in enumerate(fanouts):
+        wo, cols, vals, dst_g, src_g = (t.cpu().numpy() for t in hops[h])
+        assert np.array_equal(dst_g, dst) and src_g.size == n_src[h] and cols.size == tiles[h] * 8
+        nbr_r, w_r, _ = oracle.sample_hop(graph.row_ptr, graph.col_idx, graph.values, dst, f, 77, h)
+        src_r, wo_r, cols_r, vals_r = oracle.build_block(dst, nbr_r, w_r)
+        assert np.array_equal(src_g[:src_r.size], src_r) and (src_g[src_r.size:] == -1).all()
+        assert np.array_equal(wo, wo_r)
+        assert np.array_equal(cols[:cols_r.size], cols_r) and (cols[cols_r.size:] == -1).all()
+        assert np.array_equal(vals[:vals_r.size].view(np.uint32), vals_r.view(np.uint32)) and (vals[vals_r.size:] == 0).all()
+        assert counts[h].tolist() == [src_r.size, int((nbr_r >= 0).sum()), int(wo_r[-1]), int((dst >= 0).sum())]
+        dst = src_g                                        # the next frontier keeps the -1 padding
+
+
+def test_fused_blocks_train_like_exact_blocks(graph):
+    """A 3-layer GCN sees the same logits and weight gradients for the seeds through the bound-sized
+    blocks of the fused call (sampled from a CSR topology, no full-graph BCSR) as through the
+    exactly sized blocks of the hop-by-hop path; the transposed blocks are built without read-backs."""
+    from graph_rws_b200 import BCSRGraph, GCN_BCSR
+    from graph_rws_b200.data import CSRTopology
+    from graph_rws_b200.sampler import BCSRSampler
+    dev = torch.device("cuda")
+    g = BCSRGraph.from_csr(graph.num_nodes, graph.row_ptr, graph.col_idx, graph.values, device=dev)
+    topo = CSRTopology(*_dev_csr(graph))
+    x = torch.randn(graph.num_nodes, 24, generator=torch.Generator().manual_seed(3)).to(dev)
+    seeds = torch.arange(7, 2007, 10, dtype=torch.int32)
+    torch.manual_seed(5)
+    model = GCN_BCSR(24, 32, 5, num_layers=3, dropout=0.0, use_checkpoint=False).to(dev)
+    out = []
+    for sampler, gg in ((BCSRSampler([6, 4, 3], verbose=False, seed=9, fused=False), g),
+                        (BCSRSampler([6, 4, 3], verbose=False, seed=9, fused=True, pad_to=256), topo)):
+        blocks = sampler.sample_layers(gg, seeds)
+        ids = blocks[0].input_nodes.clamp(min=0)
+        model.zero_grad(set_to_none=True)
+        logits = model(blocks, x[ids.long()])[:seeds.numel()]
+        logits.square().sum().backward()
+        out.append((logits.detach().clone(), [p.grad.clone() for p in model.parameters()]))
+    torch.testing.assert_close(out[0][0], out[1][0], rtol=2e-3, atol=2e-3)      # TF32 products, other summation order
+    for a, b in zip(out[0][1], out[1][1]):
+        torch.testing.assert_close(a, b, rtol=5e-3, atol=5e-3)
