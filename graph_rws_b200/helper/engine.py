@@ -15,14 +15,64 @@ import torch.distributed as dist
 import torch.nn.functional as F
 
 
+class _FlatGrads:
+    """All gradients of a model as views into one flat buffer, so that the data-parallel all-reduce
+    is a single collective on that buffer with no gather / scatter passes around it."""
+
+    def __init__(self, params):
+        self.params = [p for p in params if p.requires_grad]
+        dtype, device = self.params[0].dtype, self.params[0].device
+        self.flat = torch.zeros(sum(p.numel() for p in self.params), dtype=dtype, device=device)
+        off = 0
+        for p in self.params:
+            p.grad = self.flat[off:off + p.numel()].view_as(p)
+            off += p.numel()
+
+    def valid(self):
+        return all(p.grad is not None and p.grad.untyped_storage().data_ptr() == self.flat.untyped_storage().data_ptr()
+                   for p in self.params)
+
+
+def _flat_grads(model):
+    params = list(model.parameters())
+    fg = getattr(model, '_grws_flat_grads', None)
+    if fg is None or not fg.valid() or len({p.dtype for p in params}) != 1:
+        if len({p.dtype for p in params}) != 1 or not params:
+            return None
+        fg = _FlatGrads(params)
+        try:
+            model._grws_flat_grads = fg
+        except AttributeError:
+            pass
+    return fg
+
+
+def _zero_grads(model, optimizer):
+    """Gradients := 0, kept as views of one flat buffer when the model allows it."""
+    fg = _flat_grads(model) if hasattr(model, 'parameters') else None
+    if fg is None:
+        optimizer.zero_grad(set_to_none=True)
+    else:
+        fg.flat.zero_()
+
+
 def _allreduce_grads(model, group=None, average=True):
     if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size(group) == 1:
+        return
+    from ..parallel.row_partition import collective_timers
+    fg = getattr(model, '_grws_flat_grads', None)
+    if fg is not None and fg.valid():
+        with collective_timers.timed("all_reduce", fg.flat.device):
+            dist.all_reduce(fg.flat, group=group)
+        if average:
+            fg.flat /= dist.get_world_size(group)
         return
     grads = [p.grad for p in model.parameters() if p.grad is not None]
     if not grads:
         return
     flat = torch.cat([g.reshape(-1) for g in grads])
-    dist.all_reduce(flat, group=group)
+    with collective_timers.timed("all_reduce", flat.device):
+        dist.all_reduce(flat, group=group)
     if average:
         flat /= dist.get_world_size(group)
     off = 0
@@ -34,7 +84,7 @@ def _allreduce_grads(model, group=None, average=True):
 def train_step_full(model, graph, features, labels, train_idx, optimizer):
     """One full-graph epoch (= one step); returns the loss tensor (no host sync)."""
     model.train()
-    optimizer.zero_grad(set_to_none=True)
+    _zero_grads(model, optimizer)
     logits = model(graph, features)
     loss = F.cross_entropy(logits[train_idx].float(), labels[train_idx])
     loss.backward()
@@ -49,7 +99,7 @@ def train_step_full_sharded(model, graph, features_local, labels_local, train_id
     (``graph`` is a parallel.RowShardedGraph).  The loss is the global mean over ``num_train``
     training rows: every rank sums its own rows' terms, so the weight gradients ADD across ranks."""
     model.train()
-    optimizer.zero_grad(set_to_none=True)
+    _zero_grads(model, optimizer)
     logits = model(graph, features_local)
     loss = F.cross_entropy(logits[train_idx_local].float(), labels_local[train_idx_local], reduction='sum') / num_train
     loss.backward()
@@ -59,16 +109,40 @@ def train_step_full_sharded(model, graph, features_local, labels_local, train_id
     return loss.detach()
 
 
+def layer0_inputs(blocks, features, fetch_rows=None):
+    """(blocks, x) to hand to the model for a sampled step.
+
+    With sharded features the rows of the input nodes are fetched (``fetch_rows``: the real node ids
+    only, padding entries get zero rows).  With the whole feature matrix on this GPU nothing is
+    gathered at all: the first block gets its column ids rewritten to global node ids (one gather
+    over the block's ids) and the product reads the feature rows in place -- the reference
+    multiplies and gathers over every row of the matrix instead (layers/layer.py:40,
+    helper/engine.py:170-171)."""
+    import copy
+    b0 = blocks[0]
+    if fetch_rows is not None:
+        ids = b0.input_nodes
+        real = ids >= 0
+        x = torch.zeros((ids.numel(), features.shape[1]), dtype=features.dtype, device=features.device)
+        x[real] = fetch_rows(ids[real])
+        return blocks, x
+    g0 = copy.copy(b0)
+    cols = b0.original_col_indices
+    g0.original_col_indices = torch.where(cols >= 0, b0.input_nodes[cols.clamp(min=0).long()], cols)
+    g0.self_rows = b0.output_nodes.clamp(min=0).long()
+    g0.num_cols = features.shape[0]
+    g0._shared = {}
+    return [g0] + list(blocks[1:]), features
+
+
 def train_step_sampled(model, sampler, graph, features, labels, seeds, optimizer, fetch_rows=None):
     """One mini-batch step: sample the blocks for ``seeds``, gather the input rows, train.
 
     ``fetch_rows(node_ids)`` supplies feature rows when they are sharded across ranks
     (parallel.exchange_rows); by default they are indexed from the local ``features``."""
     model.train()
-    blocks = sampler.sample_layers(graph, seeds)
-    ids = blocks[0].input_nodes.clamp(min=0)        # padding entries (-1) fetch row 0; nothing refers to them
-    x = fetch_rows(ids) if fetch_rows is not None else features[ids.long()]
-    optimizer.zero_grad(set_to_none=True)
+    blocks, x = layer0_inputs(sampler.sample_layers(graph, seeds), features, fetch_rows)
+    _zero_grads(model, optimizer)
     logits = model(blocks, x)[:seeds.numel()]
     loss = F.cross_entropy(logits.float(), labels[seeds.long()])
     loss.backward()
@@ -121,13 +195,11 @@ def train_epoch_node_sampling(model, graph, features, labels, train_idx, optimiz
     def make_batch(step, lo):
         seeds = train_idx[lo:lo + batch_size].to(device=device, dtype=torch.int32, non_blocking=True)
         sampler.step = step
-        blocks = sampler.sample_layers(graph, seeds)
-        ids = blocks[0].input_nodes.clamp(min=0)
-        x = fetch_rows(ids) if fetch_rows is not None else features[ids.long()]
+        blocks, x = layer0_inputs(sampler.sample_layers(graph, seeds), features, fetch_rows)
         return seeds, blocks, x
 
     def train_on(seeds, blocks, x):
-        optimizer.zero_grad(set_to_none=True)
+        _zero_grads(model, optimizer)
         logits = model(blocks, x)[:seeds.numel()]
         loss = F.cross_entropy(logits.float(), labels[seeds.long()])
         loss.backward()

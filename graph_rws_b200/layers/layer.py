@@ -65,6 +65,29 @@ class BCSRSPMMFunction(Function):
         return None, grad_features, grad_weight, None
 
 
+class BCSRAggregateFirstFunction(Function):
+    """``(A @ X) @ W`` for an input ``X`` that needs no gradient (the features of the first layer).
+
+    Same value as ``A @ (X @ W)`` (layers/layer.py:40-49 of the reference computes the latter, over
+    every row of X), but the SpMM runs at the narrower width when ``in_feats <= out_feats``, and
+    the backward pass needs no transposed product at all: ``dW = (A X)^T dY`` is one small GEMM over
+    the layer's output rows.  For a sampled block this removes the largest transposed block of the
+    step (as many rows as the hop has input nodes) and its construction."""
+
+    @staticmethod
+    def forward(ctx, graph, features, weight, warps_per_block):
+        aggregated = _spmm_graph(graph, features)
+        record_spmm_time(0.0)
+        ctx.save_for_backward(aggregated, weight)
+        return torch.matmul(aggregated, weight)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        aggregated, weight = ctx.saved_tensors
+        grad_weight = torch.matmul(aggregated.t(), grad_output) if ctx.needs_input_grad[2] else None
+        return None, None, grad_weight, None
+
+
 class BCSRGraphConv(nn.Module):
     """Aggregation only; activation, normalisation and dropout live in the model."""
 
@@ -82,7 +105,10 @@ class BCSRGraphConv(nn.Module):
         nn.init.xavier_uniform_(self.weight_self)
 
     def forward(self, graph, features: torch.Tensor, features_target: torch.Tensor = None) -> torch.Tensor:
-        h_neigh = BCSRSPMMFunction.apply(graph, features, self.weight_neigh, self.warps_per_block)
+        aggregate_first = (not features.requires_grad and features.shape[1] <= self.out_feats
+                           and not hasattr(graph, 'gather_dense') and not core._timing_enabled)
+        fn = BCSRAggregateFirstFunction if aggregate_first else BCSRSPMMFunction
+        h_neigh = fn.apply(graph, features, self.weight_neigh, self.warps_per_block)
         target_rows = h_neigh.shape[0]
         if features_target is not None:
             h_in_self = features_target

@@ -12,8 +12,9 @@ Graph handling per layer follows models/model.py:96-210:
     ``reindex_bcsr``;
   * a row shard of a full graph (parallel.RowShardedGraph) keeps its global column ids; the
     layer all-gathers the feature rows of all ranks before the product;
-  * the rows fed to the self path are gathered by window when ``active_windows`` exist, else the
-    target-first slice ``h[:target_rows]`` (what per-seed sampled blocks use).
+  * the rows fed to the self path are gathered by window when ``active_windows`` exist, by the
+    block's ``self_rows`` index when its columns are global ids, else the target-first slice
+    ``h[:target_rows]`` (what per-seed sampled blocks use).
 """
 import copy
 from typing import List, Union
@@ -109,6 +110,9 @@ class GCN_BCSR(nn.Module):
 
     def _get_residual(self, layer_idx, curr_g, prev_g, h_in, target_rows):
         """Rows of ``h_in`` aligned with the layer's output rows (models/model.py:145-210)."""
+        self_rows = getattr(curr_g, 'self_rows', None)
+        if layer_idx == 0 and self_rows is not None:
+            return h_in[self_rows]          # a block whose columns are global ids names its own rows
         if h_in.shape[0] == target_rows:
             return h_in
         device = h_in.device

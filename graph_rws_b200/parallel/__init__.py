@@ -13,6 +13,6 @@ hot path shards naturally:
 Nothing here issues a TMA multicast load, and no kernel is handed a peer GPU's memory: remote
 rows land in local HBM through the collective first.
 """
-from .row_partition import (RowPartition, all_gather_rows, partition_windows_by_tiles,  # noqa: F401
-                            shard_bcsr, DistributedSpMM, RowShardedGraph)
+from .row_partition import (RowPartition, all_gather_rows, all_gather_rows_padded, collective_timers,  # noqa: F401
+                            partition_windows_by_tiles, shard_bcsr, DistributedSpMM, RowShardedGraph)
 from .seed_shard import exchange_rows, owner_of, shard_seeds  # noqa: F401

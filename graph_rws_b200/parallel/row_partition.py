@@ -6,6 +6,52 @@ import torch
 import torch.distributed as dist
 
 
+class _CollectiveTimers:
+    """Optional CUDA-event timing of the collectives on the path (off by default: the extra events
+    cost a little).  ``start()``, run some steps, ``stop()`` returns the milliseconds spent per
+    collective kind on the launching stream -- what a benchmark needs to say which part of an
+    epoch is communication."""
+
+    def __init__(self):
+        self.on = False
+        self.pairs = []
+
+    def start(self):
+        self.on, self.pairs = True, []
+
+    def stop(self):
+        self.on = False
+        out = {}
+        for name, a, b in self.pairs:
+            b.synchronize()
+            out[name] = out.get(name, 0.0) + a.elapsed_time(b)
+        self.pairs = []
+        return out
+
+    class _Span:
+        def __init__(self, owner, name, device):
+            self.owner, self.name, self.device = owner, name, device
+
+        def __enter__(self):
+            if self.owner.on and self.device.type == 'cuda':
+                self.a = torch.cuda.Event(enable_timing=True)
+                self.a.record()
+            return self
+
+        def __exit__(self, *exc):
+            if self.owner.on and self.device.type == 'cuda':
+                b = torch.cuda.Event(enable_timing=True)
+                b.record()
+                self.owner.pairs.append((self.name, self.a, b))
+            return False
+
+    def timed(self, name, device):
+        return self._Span(self, name, torch.device(device))
+
+
+collective_timers = _CollectiveTimers()
+
+
 @dataclass
 class RowPartition:
     """Contiguous window range [w_begin, w_end) of every rank and the matching row ranges."""
@@ -25,6 +71,17 @@ class RowPartition:
 
     def max_rows(self) -> int:
         return max(self.rows(r)[1] - self.rows(r)[0] for r in range(self.world))
+
+    def padded_ids(self, ids: torch.Tensor) -> torch.Tensor:
+        """Row ids in the padded numbering of ``all_gather_rows_padded``: rank r's rows start at
+        ``r * max_rows()``.  Negative ids (padding) stay as they are.  The map is increasing, so
+        sorted column lists stay sorted."""
+        starts = torch.tensor([self.rows(r)[0] for r in range(self.world)], dtype=torch.int64, device=ids.device)
+        ends = torch.tensor([self.rows(r)[1] for r in range(self.world)], dtype=torch.int64, device=ids.device)
+        idl = ids.to(torch.int64)
+        owner = torch.bucketize(idl, ends, right=True).clamp_(max=self.world - 1)
+        out = owner * self.max_rows() + (idl - starts[owner])
+        return torch.where(idl < 0, idl, out).to(ids.dtype)
 
 
 def partition_windows_by_tiles(window_offset: torch.Tensor, world: int, num_rows: Optional[int] = None) -> RowPartition:
@@ -66,7 +123,8 @@ def all_gather_rows(local: torch.Tensor, part: RowPartition, group=None) -> torc
         send = torch.zeros((pad_rows, n), dtype=local.dtype, device=local.device)
         send[:local.shape[0]] = local
     recv = torch.empty((world * pad_rows, n), dtype=local.dtype, device=local.device)
-    dist.all_gather_into_tensor(recv, send.contiguous(), group=group)
+    with collective_timers.timed("all_gather", local.device):
+        dist.all_gather_into_tensor(recv, send.contiguous(), group=group)
     if all(part.rows(r)[1] - part.rows(r)[0] == pad_rows for r in range(world)):
         return recv[:part.num_rows]
     full = torch.empty((part.num_rows, n), dtype=local.dtype, device=local.device)
@@ -74,6 +132,28 @@ def all_gather_rows(local: torch.Tensor, part: RowPartition, group=None) -> torc
         lo, hi = part.rows(r)
         full[lo:hi] = recv[r * pad_rows:r * pad_rows + (hi - lo)]
     return full
+
+
+def all_gather_rows_padded(local: torch.Tensor, part: RowPartition, group=None) -> torch.Tensor:
+    """All-gather the row shards into a [world * max_rows, N] matrix in which rank r's rows start at
+    ``r * max_rows`` (``RowPartition.padded_ids`` gives the numbering).  Nothing is copied out
+    afterwards: the consumer's column ids are rewritten to this numbering once, when the graph is
+    sharded, so the product reads the receive buffer directly.  The rows between a rank's last row
+    and the next rank's first are never referenced."""
+    world = part.world
+    pad_rows = part.max_rows()
+    n = local.shape[1]
+    if world == 1:
+        return local
+    send = local
+    if local.shape[0] != pad_rows:
+        send = torch.empty((pad_rows, n), dtype=local.dtype, device=local.device)
+        send[:local.shape[0]] = local
+        send[local.shape[0]:] = 0
+    recv = torch.empty((world * pad_rows, n), dtype=local.dtype, device=local.device)
+    with collective_timers.timed("all_gather", local.device):
+        dist.all_gather_into_tensor(recv, send.contiguous(), group=group)
+    return recv
 
 
 class DistributedSpMM:
@@ -109,12 +189,17 @@ class RowShardedGraph:
     def __init__(self, local, part: RowPartition, rank: int, local_t=None, group=None):
         self.local, self.part, self.rank, self.group = local, part, rank, group
         self._local_t = local_t
+        # column ids in the padded numbering of the all-gathered operand (done once, here): the
+        # product then reads the receive buffer of the all-gather without a compaction pass
+        if part.world > 1 and not getattr(local, '_padded_cols', False):
+            local.original_col_indices = part.padded_ids(local.original_col_indices)
+            local._padded_cols = True
         for name in ("window_offset", "original_col_indices", "values_condensed", "tile_rows", "tile_cols",
                      "num_windows", "device"):
             setattr(self, name, getattr(local, name))
         lo, hi = part.rows(rank)
         self.num_rows = self.num_nodes = hi - lo
-        self.num_cols = part.num_rows
+        self.num_cols = part.world * part.max_rows() if part.world > 1 else part.num_rows
         self._shared = local._shared
 
     @classmethod
@@ -136,7 +221,7 @@ class RowShardedGraph:
 
     def gather_dense(self, dense_local):
         # a product returns whole windows: rows past the rank's last row are padding
-        return all_gather_rows(dense_local[:self.num_rows], self.part, self.group)
+        return all_gather_rows_padded(dense_local[:self.num_rows], self.part, self.group)
 
     def transposed(self, num_cols=None, dtype=None):
         if self._local_t is None:

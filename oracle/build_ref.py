@@ -17,7 +17,14 @@ import os
 import sys
 
 
-def build(ref_root: str = "/root/reference", verbose: bool = False):
+def default_reference_root() -> str:
+    """GRWS_REFERENCE_ROOT, else a checkout named `reference` next to this repository."""
+    here = os.path.dirname(os.path.abspath(__file__))
+    return os.environ.get("GRWS_REFERENCE_ROOT") or os.path.join(os.path.dirname(os.path.dirname(here)), "reference")
+
+
+def build(ref_root: str = None, verbose: bool = False):
+    ref_root = ref_root or default_reference_root()
     import torch  # noqa: F401
     from torch.utils import cpp_extension
 
@@ -59,4 +66,4 @@ def load():
 
 
 if __name__ == "__main__":
-    print(build(sys.argv[1] if len(sys.argv) > 1 else "/root/reference", verbose=True))
+    print(build(sys.argv[1] if len(sys.argv) > 1 else None, verbose=True))

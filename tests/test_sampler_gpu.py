@@ -207,3 +207,28 @@ def test_fused_blocks_train_like_exact_blocks(graph):
     torch.testing.assert_close(out[0][0], out[1][0], rtol=2e-3, atol=2e-3)      # TF32 products, other summation order
     for a, b in zip(out[0][1], out[1][1]):
         torch.testing.assert_close(a, b, rtol=5e-3, atol=5e-3)
+
+
+def test_first_block_with_global_ids_equals_gathered_rows(graph):
+    """helper.layer0_inputs: reading the feature rows in place through global column ids gives the
+    logits and weight gradients of the gather-then-multiply path."""
+    from graph_rws_b200 import GCN_BCSR
+    from graph_rws_b200.data import CSRTopology
+    from graph_rws_b200.helper import layer0_inputs
+    from graph_rws_b200.sampler import BCSRSampler
+    dev = torch.device("cuda")
+    topo = CSRTopology(*_dev_csr(graph), block_dtype=torch.float16)
+    x = torch.randn(graph.num_nodes, 128, generator=torch.Generator().manual_seed(3)).half().to(dev)
+    seeds = torch.arange(3, 1803, 9, dtype=torch.int32)
+    torch.manual_seed(6)
+    model = GCN_BCSR(128, 128, 7, num_layers=3, dropout=0.0, use_checkpoint=False).to(dev).half()
+    blocks = BCSRSampler([5, 4, 3], verbose=False, seed=3, pad_to=256).sample_layers(topo, seeds)
+    out = []
+    for bl, xx in ((blocks, x[blocks[0].input_nodes.clamp(min=0).long()]), layer0_inputs(blocks, x)):
+        model.zero_grad(set_to_none=True)
+        logits = model(bl, xx)[:seeds.numel()]
+        logits.float().square().sum().backward()
+        out.append((logits.detach().float(), [p.grad.float().clone() for p in model.parameters()]))
+    torch.testing.assert_close(out[0][0], out[1][0], rtol=1e-2, atol=1e-2)
+    for a, b in zip(out[0][1], out[1][1]):
+        torch.testing.assert_close(a, b, rtol=2e-2, atol=2e-2)
