@@ -705,7 +705,16 @@ def secondary_sampled(args, torch, scale=1.0, steps=10):
     sampler = BCSRSampler([15, 10, 5], verbose=False, pad_to=256)          # fused: one call per step, no read-backs
     per_gpu = 1024
     state = {"i": 0}
-    fetch = (lambda ids: exchange_rows(x_local, ids, n)) if world > 1 else None
+    fetch, feature_path = None, "local"
+    if world > 1:
+        try:
+            from graph_rws_b200.parallel import ShardedFeatures
+            fetch = ShardedFeatures(x_local, n)
+            feature_path = "row-sharded over %d ranks, rows read from the owners' memory over NVLink (one gather kernel per step)" % world
+        except Exception as exc:          # noqa: BLE001  (no peer-addressable memory on this box)
+            sys.stderr.write(f"bench.py: peer-memory feature store unavailable ({exc}); using the all-to-all exchange\n")
+            fetch = lambda ids: exchange_rows(x_local, ids, n)   # noqa: E731
+            feature_path = "row-sharded over %d ranks, index + row all-to-all inside the step" % world
 
     def seeds_for_step():
         s0 = ((state["i"] * world + rank) * per_gpu) % max(train.numel() - per_gpu, 1)
@@ -753,7 +762,7 @@ def secondary_sampled(args, torch, scale=1.0, steps=10):
            "ms_per_step": step_ms, "sampling_only_seeds_per_s": world * per_gpu / (samp_ms * 1e-3), "sampling_ms": samp_ms,
            "n": world, "scaling": "weak", "scale": scale, "nodes": n, "nnz": nnz, "fanouts": [15, 10, 5], "seeds_per_gpu": per_gpu,
            "hidden": 256, "dtype": "f16", "topology": "CSR replicated per GPU, no full-graph BCSR",
-           "features": "row-sharded over %d ranks, index + row all-to-all inside the step" % world if world > 1 else "local",
+           "features": feature_path,
            "hop_counts": [{"frontier": c[3], "edges": c[1], "tiles": c[2], "sources": c[0]} for c in counts],
            "roofline": {"bound": "hbm", "kernel": "sampling + dedup + block build (all hops of a step)", "achieved": achieved,
                         "peak": peak, "peak_source": peak_kind, "unit": "GB/s", "frac": achieved / peak,

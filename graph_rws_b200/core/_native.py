@@ -50,6 +50,7 @@ SIGNATURES = {
     "grws_sample_layers_scratch_bytes": (c_sz, [c_i64, c_vp, c_i32, c_i64]),
     "grws_sample_layers": (c_i32, [c_vp, c_vp, c_vp, c_vp, c_i64, c_vp, c_i32, ctypes.c_uint64, c_vp, c_i64, c_i32,
                                    c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_sz, c_vp]),
+    "grws_gather_rows_sharded": (c_i32, [c_vp, c_i32, c_i64, c_i64, c_i64, c_vp, c_i64, c_vp, c_vp]),
     "grws_reindex_bcsr": (c_i32, [c_vp, c_vp, c_i32, c_vp, c_i64, c_i64, c_i32, c_i32, c_vp, c_vp]),
 }
 

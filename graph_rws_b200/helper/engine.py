@@ -122,9 +122,12 @@ def layer0_inputs(blocks, features, fetch_rows=None):
     b0 = blocks[0]
     if fetch_rows is not None:
         ids = b0.input_nodes
+        if hasattr(fetch_rows, 'gather'):           # a row store that takes padding ids itself (zero rows)
+            return blocks, fetch_rows.gather(ids)
         real = ids >= 0
-        x = torch.zeros((ids.numel(), features.shape[1]), dtype=features.dtype, device=features.device)
-        x[real] = fetch_rows(ids[real])
+        rows = fetch_rows(ids[real])
+        x = torch.zeros((ids.numel(), rows.shape[1]), dtype=rows.dtype, device=rows.device)
+        x[real] = rows
         return blocks, x
     g0 = copy.copy(b0)
     cols = b0.original_col_indices

@@ -16,3 +16,4 @@ rows land in local HBM through the collective first.
 from .row_partition import (RowPartition, all_gather_rows, all_gather_rows_padded, collective_timers,  # noqa: F401
                             partition_windows_by_tiles, shard_bcsr, DistributedSpMM, RowShardedGraph)
 from .seed_shard import exchange_rows, owner_of, shard_seeds  # noqa: F401
+from .feature_store import ShardedFeatures  # noqa: F401,E402

@@ -282,6 +282,19 @@ int grws_sample_layers(const int64_t *row_ptr, const int32_t *col_idx, const flo
                        void *scratch, size_t scratch_bytes, void *stream);
 
 /* ------------------------------------------------------------------------------------------
+ * Rows of a feature matrix that is sharded over the GPUs of one node, read from their owners over
+ * NVLink with plain loads.  Replaces the reference's placement of large feature matrices in pinned
+ * host memory with a CPU-side gather per step (helper/engine.py:135-147,
+ * data/data_loader.py:1513-1564).  Rank r owns rows [r * rows_per_shard, (r+1) * rows_per_shard);
+ * `shards` is a DEVICE array of `world` pointers to the ranks' blocks, each addressable from this
+ * GPU (peer-mapped or local), rows src_stride_bytes apart.  out[i] = row ids[i] (row_bytes each,
+ * packed); ids[i] < 0 gives a zero row.  row_bytes and src_stride_bytes are multiples of 16.
+ * ------------------------------------------------------------------------------------------ */
+int grws_gather_rows_sharded(const void *const *shards, int world, int64_t rows_per_shard,
+                             int64_t row_bytes, int64_t src_stride_bytes, const int32_t *ids,
+                             int64_t n, void *out, void *stream);
+
+/* ------------------------------------------------------------------------------------------
  * Global -> local column ids by window lookup, pruning misses.  Replaces reindex_bcsr_cuda +
  * reindex_and_prune_kernel (core/wrapper/reindex_wrapper.cu:27-68, core/include/reindex.cuh:
  * 33-102) with identical integer arithmetic: window = col / tile_rows (C division, so -1 maps

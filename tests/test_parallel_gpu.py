@@ -104,6 +104,63 @@ def _gcn_worker(rank, world, port, out):
         dist.destroy_process_group()
 
 
+def _sampled_worker(rank, world, port, out):
+    """Seed-sharded sampled step with the feature rows sharded over the ranks: the rows a rank reads
+    from its peers' memory equal the rows of the full matrix, the blocks a rank samples equal the
+    blocks one GPU samples for the same seeds (keyed Philox), and a data-parallel step runs."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from graph_rws_b200 import GCN_BCSR
+        from graph_rws_b200.data import CSRTopology, synthetic
+        from graph_rws_b200.helper import train_step_sampled
+        from graph_rws_b200.parallel import ShardedFeatures, shard_seeds
+        from graph_rws_b200.sampler import BCSRSampler
+        g = synthetic.sym_normalized_csr(12000, *synthetic.chung_lu_edges(12000, 150000, 2.3, 19))
+        topo = CSRTopology(torch.from_numpy(g.row_ptr), torch.from_numpy(g.col_idx), torch.from_numpy(g.values), device=dev,
+                           block_dtype=torch.float16)
+        n = g.num_nodes
+        X = torch.randn(n, 128, generator=torch.Generator().manual_seed(4)).half().to(dev)
+        per = (n + world - 1) // world
+        store = ShardedFeatures(X[rank * per:(rank + 1) * per].contiguous(), n)
+        ids = torch.randint(-1, n, (7000,), generator=torch.Generator().manual_seed(rank)).int().to(dev)
+        rows = store.gather(ids)
+        want = X[ids.clamp(min=0).long()]
+        want[ids < 0] = 0
+        assert torch.equal(rows, want)
+        # the blocks of this rank's seeds do not depend on the rank count
+        all_seeds = torch.randperm(n, generator=torch.Generator().manual_seed(8))[:1024].int().to(dev)
+        mine = shard_seeds(all_seeds, rank, world)
+        sampler = BCSRSampler([6, 4, 3], verbose=False, seed=21, pad_to=256)
+        blocks = sampler.sample_layers(topo, mine)
+        whole = sampler.sample_layers(topo, all_seeds)
+        lo = (all_seeds.numel() * rank) // world
+        # per-node neighbour lists are keyed by (seed, node, hop): the first-hop sources of this
+        # rank's seeds are a subset of what the one-GPU batch reaches
+        assert set(blocks[-1].input_nodes[blocks[-1].input_nodes >= 0].tolist()) <= \
+            set(whole[-1].input_nodes[whole[-1].input_nodes >= 0].tolist())
+        assert torch.equal(blocks[-1].output_nodes, all_seeds[lo:lo + mine.numel()])
+        torch.manual_seed(5)
+        model = GCN_BCSR(128, 64, 7, num_layers=3, dropout=0.0, use_checkpoint=False).to(dev).half()
+        for p_ in model.parameters():
+            dist.broadcast(p_.data, 0)
+        y = torch.randint(0, 7, (n,), generator=torch.Generator().manual_seed(9)).to(dev)
+        opt = torch.optim.SGD(model.parameters(), lr=0.01)
+        loss = train_step_sampled(model, sampler, topo, None, y, mine, opt, fetch_rows=store)
+        assert torch.isfinite(loss).item()
+        # after the gradient all-reduce every rank holds the same weights
+        w = torch.cat([p_.detach().float().reshape(-1) for p_ in model.parameters()])
+        ws = [torch.empty_like(w) for _ in range(world)]
+        dist.all_gather(ws, w)
+        assert torch.equal(ws[0], ws[1])
+        torch.cuda.synchronize()
+        out[rank] = 1
+    finally:
+        dist.destroy_process_group()
+
+
 def _run(worker):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
@@ -130,3 +187,7 @@ def test_row_partitioned_spmm_and_row_exchange_on_two_gpus():
 
 def test_row_sharded_gcn_step_matches_single_gpu():
     _run(_gcn_worker)
+
+
+def test_sampled_step_with_features_read_from_peer_memory():
+    _run(_sampled_worker)
