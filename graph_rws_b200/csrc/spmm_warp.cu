@@ -133,7 +133,7 @@ __device__ __forceinline__ StepCols load_cols(const int32_t *__restrict__ cols, 
 template <int DT, int NG>
 __device__ __forceinline__ void load_step(StepData<DT, NG> &d, const StepCols &sc,
                                           const void *__restrict__ vals, const void *__restrict__ B,
-                                          int64_t ldb, int64_t N, int64_t n0, int64_t seg_s,
+                                          int64_t ldb, int64_t K, int64_t N, int64_t n0, int64_t seg_s,
                                           int64_t seg_e, int64_t p, int g, int t, uint64_t keep,
                                           uint64_t stream) {
     using G = StepGeom<DT>;
@@ -144,7 +144,8 @@ __device__ __forceinline__ void load_step(StepData<DT, NG> &d, const StepCols &s
         for (int gi = 0; gi < NG; ++gi) {
             const int64_t feat = n0 + gi * G::kGroup + g * (16 / G::kElem);
             uint4 v = make_uint4(0u, 0u, 0u, 0u);
-            if (sc.c[r] >= 0 && feat < N) v = ldg128_hint(Bb + ((int64_t)sc.c[r] * ldb + feat) * G::kElem, keep);
+            // ids outside [0, K) -- the -1 padding, an id past the operand -- contribute nothing
+            if ((uint64_t)(int64_t)sc.c[r] < (uint64_t)K && feat < N) v = ldg128_hint(Bb + ((int64_t)sc.c[r] * ldb + feat) * G::kElem, keep);
             d.h[r * NG + gi] = v;
         }
     }
@@ -285,16 +286,16 @@ spmm_warp_kernel(const SpmmWarpParams prm) {
             {
                 StepCols c0 = load_cols<DT>(prm.cols, seg_s, seg_e, 0, t, stream);
                 StepCols c1 = load_cols<DT>(prm.cols, seg_s, seg_e, 1, t, stream);
-                load_step<DT, NG>(d0, c0, prm.vals, prm.B, prm.ldb, N, n0, seg_s, seg_e, 0, g, t, keep, stream);
-                load_step<DT, NG>(d1, c1, prm.vals, prm.B, prm.ldb, N, n0, seg_s, seg_e, 1, g, t, keep, stream);
+                load_step<DT, NG>(d0, c0, prm.vals, prm.B, prm.ldb, prm.K, N, n0, seg_s, seg_e, 0, g, t, keep, stream);
+                load_step<DT, NG>(d1, c1, prm.vals, prm.B, prm.ldb, prm.K, N, n0, seg_s, seg_e, 1, g, t, keep, stream);
             }
             for (int64_t p = 0; p < nsteps; p += 2) {
                 StepCols c4 = load_cols<DT>(prm.cols, seg_s, seg_e, p + 4, t, stream);
                 StepCols c5 = load_cols<DT>(prm.cols, seg_s, seg_e, p + 5, t, stream);
                 mma_step<DT, NG>(acc, d0);
-                load_step<DT, NG>(d0, c2, prm.vals, prm.B, prm.ldb, N, n0, seg_s, seg_e, p + 2, g, t, keep, stream);
+                load_step<DT, NG>(d0, c2, prm.vals, prm.B, prm.ldb, prm.K, N, n0, seg_s, seg_e, p + 2, g, t, keep, stream);
                 if (p + 1 < nsteps) mma_step<DT, NG>(acc, d1);
-                load_step<DT, NG>(d1, c3, prm.vals, prm.B, prm.ldb, N, n0, seg_s, seg_e, p + 3, g, t, keep, stream);
+                load_step<DT, NG>(d1, c3, prm.vals, prm.B, prm.ldb, prm.K, N, n0, seg_s, seg_e, p + 3, g, t, keep, stream);
                 c2 = c4;
                 c3 = c5;
             }
@@ -363,7 +364,12 @@ spmm_fixup_kernel(const SpmmWarpParams prm) {
 // host side
 // ---------------------------------------------------------------------------------------------
 void spmm_warp_plan(int64_t num_tiles_bound, int64_t *n_items, int64_t *chunk, int64_t *long_window) {
-    const int64_t target_items = 16384;
+    // work items (one warp each): 112 per SM, i.e. 14 waves of the 8-warp CTAs -- enough for the
+    // power-law tail to even out, few enough that the per-item partial tiles stay small
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+        sms = 148;
+    const int64_t target_items = (int64_t)sms * 112;
     int64_t c = ceil_div(num_tiles_bound > 0 ? num_tiles_bound : 1, target_items);
     if (c < 64) c = 64;
     c = (c + 1) & ~int64_t(1);
@@ -379,10 +385,14 @@ size_t spmm_warp_scratch_bytes(int64_t num_tiles_bound, int64_t N) {
     return (size_t)n_items * 2 * TILE_ROWS * (size_t)N * sizeof(float);
 }
 
-// GRWS_WARP_NARROW=1 gives every warp a single feature group (more warps per SM, A read per group)
+// experiment builds (-DGRWS_WARP_NARROW=1) give every warp a single feature group (more warps per
+// SM, the A fragments read once per group)
 static bool narrow_slabs() {
-    static const int v = [] { const char *e = getenv("GRWS_WARP_NARROW"); return e ? atoi(e) : 0; }();
-    return v != 0;
+#ifdef GRWS_WARP_NARROW
+    return GRWS_WARP_NARROW != 0;
+#else
+    return false;
+#endif
 }
 
 template <int DT>

@@ -132,3 +132,50 @@ def test_pipelined_epoch_equals_serial_epoch():
     assert abs(out[0] - out[1]) < 1e-3 * abs(out[0]), out
     for pa, pb in zip(model_a.parameters(), model_b.parameters()):
         assert torch.allclose(pa, pb, rtol=1e-3, atol=1e-4)
+
+
+def test_window_style_graphs_with_active_windows(oracle, small):
+    """Graphs in the reference sampler's format -- rows are whole 16-row windows of the global graph,
+    column ids are global, ``active_windows`` names the windows (sampler/sampler.py:261-277) -- go
+    through the model's window branches: the layer-0 self rows gathered by window, the per-layer
+    ``reindex_bcsr`` against the previous graph's windows, the window lookup of the later self rows
+    (models/model.py:118-143,183-194).  With every tile of the chosen windows kept, the result on
+    those windows equals the full-graph forward pass."""
+    from graph_rws_b200 import BCSRGraph, GCN_BCSR
+    g, graph, A = small
+    dev = torch.device("cuda")
+    wo = graph.window_offset.cpu().numpy()
+    cols = graph.original_col_indices.cpu().numpy().reshape(-1, 8)
+    vals = graph.values_condensed.cpu().numpy().reshape(-1, 128)
+
+    def window_subgraph(wins):
+        tiles = np.concatenate([np.arange(wo[w], wo[w + 1]) for w in wins])
+        sub_wo = np.concatenate([[0], np.cumsum([wo[w + 1] - wo[w] for w in wins])]).astype(np.int64)
+        sub = BCSRGraph.from_components(torch.from_numpy(sub_wo).to(dev), torch.from_numpy(cols[tiles].reshape(-1)).to(dev),
+                                        torch.from_numpy(vals[tiles].reshape(-1)).to(dev), num_rows=len(wins) * 16,
+                                        num_cols=g.num_nodes, tile_rows=16, tile_cols=8, device=dev)
+        sub.active_windows = torch.from_numpy(np.asarray(wins, dtype=np.int32)).to(dev)
+        return sub
+
+    seeds = np.random.default_rng(2).permutation(2600)[:40].astype(np.int32)
+    win1, masks = oracle.windows_and_masks(seeds)                   # sorted unique windows of the seeds
+    assert win1.size < seeds.size + 1 and (np.diff(win1) > 0).all() and masks.size == win1.size
+    g1 = window_subgraph(win1)
+    c1 = g1.original_col_indices.cpu().numpy()
+    win0 = np.unique(c1[c1 >= 0] // 16).astype(np.int32)           # every window the output layer reads from
+    assert np.isin(win1, win0).all()                                # self-loops: a window is among its own sources
+    g0 = window_subgraph(win0)
+    torch.manual_seed(4)
+    model = GCN_BCSR(40, 24, 5, num_layers=2, dropout=0.0, use_checkpoint=False).to(dev)
+    x = torch.randn(g.num_nodes, 40, generator=torch.Generator().manual_seed(5)).to(dev)
+    model.eval()
+    with torch.no_grad():
+        full = model(graph, x)                                     # [num_nodes, 5], checked against dense algebra above
+        sub = model([g0, g1], x)
+    assert sub.shape == (win1.size * 16, 5)
+    rows = (win1[:, None].astype(np.int64) * 16 + np.arange(16)[None, :]).reshape(-1)
+    keep = rows < g.num_nodes
+    got, want = sub[torch.from_numpy(np.nonzero(keep)[0]).to(dev)], full[torch.from_numpy(rows[keep]).to(dev)]
+    assert torch.allclose(got, want, rtol=2e-2, atol=2e-3), float((got - want).abs().max())
+    # the output layer's column ids were localised against the first graph's windows
+    assert int(g1.original_col_indices.max()) < win0.size * 16

@@ -163,3 +163,74 @@ def test_against_reference_kernels_when_built(oracle):
     G_theirs = ref.spmm_transpose(wo, cols, vals, G, 600)
     G_ours = core.spmm_transpose(wo, cols, vals, G, 600)
     check_spmm_tolerance(G_ours.cpu().numpy(), G_theirs.cpu().numpy(), None, "vs reference spmm_transpose")
+    # reindex_bcsr: the reference's own kernel (core/include/reindex.cuh:33-102) on the same ids,
+    # hits, misses and -1 padding included; new ids and the pruned values are bit-identical
+    active = torch.unique(torch.div(cols[cols >= 0], 16, rounding_mode="floor"))[::2].int().contiguous()
+    v_theirs, v_ours = vals.clone(), vals.clone()
+    new_theirs = ref.reindex_bcsr(cols, v_theirs, active, 16, 8)
+    new_ours = core.reindex_bcsr(cols, v_ours, active, 16, 8)
+    assert torch.equal(new_ours, new_theirs) and torch.equal(v_ours, v_theirs)
+
+
+def test_full_size_spmm_mid_forward_and_transposed(oracle):
+    """The workload the headline is quoted on, at its stated size (169,343 nodes, 313,640 tiles,
+    fp16, N = 128): forward and transposed product against the CPU checker."""
+    from graph_rws_b200 import BCSRGraph, core
+    from graph_rws_b200.data import synthetic
+    dev = torch.device("cuda")
+    g = synthetic.graph_for_config("spmm_mid")
+    graph = BCSRGraph.from_csr(g.num_nodes, g.row_ptr, g.col_idx, g.values, device=dev, values_dtype=torch.float16)
+    wo, cols, vals = oracle.csr_to_bcsr(g.num_nodes, g.row_ptr, g.col_idx, g.values)
+    assert np.array_equal(graph.window_offset.cpu().numpy(), wo) and np.array_equal(graph.original_col_indices.cpu().numpy(), cols)
+    vals16 = torch.from_numpy(vals).half().float().numpy()
+    H = torch.randn(g.num_nodes, 128, generator=torch.Generator().manual_seed(2002)).half()
+    G = torch.randn(graph.num_windows * 16, 128, generator=torch.Generator().manual_seed(3002)).half()
+    C = core.spmm_raw(graph.window_offset, graph.original_col_indices, graph.values_condensed, H.to(dev), check=True)
+    check_spmm_tolerance(C.float().cpu().numpy(), oracle.spmm_fwd(wo, cols, vals16, H.float().numpy()), None, "spmm_mid forward")
+    D = core.spmm_transpose(graph.window_offset, graph.original_col_indices, graph.values_condensed, G.to(dev), g.num_nodes)
+    core.check_device_status()
+    check_spmm_tolerance(D.float().cpu().numpy(), oracle.spmm_transpose(wo, cols, vals16, G.float().numpy(), g.num_nodes), None,
+                         "spmm_mid transposed")
+
+
+@pytest.mark.parametrize("N", [256, 48])
+def test_dense_community_shape_bf16(oracle, N):
+    """The full-graph GCN configuration's graph shape at a quarter of its node count (58,241 nodes,
+    ~7.2 M non-zeros, ~120 tiles per window), bf16: width 256 takes the two-pass tcgen05 route
+    (operand above 8 MB), width 48 the warp-MMA kernel.  fp32 output, as for every bf16 case."""
+    from graph_rws_b200 import BCSRGraph, core
+    from graph_rws_b200.data import synthetic
+    dev = torch.device("cuda")
+    n = int(232965 * 0.25)
+    rp, ci, vv = synthetic.community_csr_torch(n, int((114_600_000 * 0.0625 - n) // 2), 50, 0.8, 1003, dev)
+    graph = BCSRGraph.from_csr(n, rp, ci, vv, device=dev, values_dtype=torch.bfloat16)
+    wo, cols, vals = oracle.csr_to_bcsr(n, rp.cpu().numpy(), ci.cpu().numpy(), vv.cpu().numpy())
+    assert np.array_equal(graph.window_offset.cpu().numpy(), wo)
+    assert n * N * 2 > (8 << 20) or N == 48
+    B = torch.randn(n, N, generator=torch.Generator().manual_seed(N)).bfloat16()
+    C = core.spmm_raw(graph.window_offset, graph.original_col_indices, graph.values_condensed, B.to(dev),
+                      out_dtype=torch.float32, check=True)
+    C_ref = oracle.spmm_fwd(wo, cols, torch.from_numpy(vals).bfloat16().float().numpy(), B.float().numpy())
+    check_spmm_tolerance(C.cpu().numpy(), C_ref, None, f"dense-community bf16 N={N}")
+
+
+def test_column_ids_beyond_the_operand_contribute_nothing(oracle):
+    """Ids >= K (a global-id graph multiplied with fewer rows than it names) read zeros in both
+    kernels, like the -1 padding; the warp-MMA path must not touch memory past the operand."""
+    from graph_rws_b200 import core
+    c = load_case(os.path.join(GOLDEN, "bcsr_chunglu_600.npz"))
+    dev = torch.device("cuda")
+    K = 400                                                  # the graph names columns up to 599
+    cols_ref = np.where(c["cols"] >= K, -1, c["cols"])
+    for dt, N, algo in (("f16", 128, core.ALGO_TCGEN05), ("f16", 128, core.ALGO_WARP_MMA), ("f32", 72, core.ALGO_WARP_MMA)):
+        dtype = DT[dt]
+        B = torch.randn(K, N, generator=torch.Generator().manual_seed(3)).to(dtype)
+        vals = torch.from_numpy(c["vals"]).to(dtype)
+        C = core.spmm_raw(torch.from_numpy(c["window_offset"]).to(dev), torch.from_numpy(c["cols"]).to(dev), vals.to(dev),
+                          B.to(dev), algo=algo, check=True)
+        C_ref = oracle.spmm_fwd(c["window_offset"], cols_ref, vals.float().numpy(), B.float().numpy())
+        check_spmm_tolerance(C.float().cpu().numpy(), C_ref, None, f"ids >= K, {dt} algo {algo}")
+    # an operand without rows: every id is out of range, the product is zero rows
+    Z = core.spmm_raw(torch.from_numpy(c["window_offset"]).to(dev), torch.from_numpy(c["cols"]).to(dev),
+                      torch.from_numpy(c["vals"]).half().to(dev), torch.empty(0, 128, dtype=torch.float16, device=dev))
+    assert Z.shape == (38 * 16, 128) and not Z.any()
