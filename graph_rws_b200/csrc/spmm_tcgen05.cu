@@ -78,7 +78,15 @@ constexpr int NUM_PRODUCER_WARPS = GRWS_TC5_STAGES;  // one per ring slot
 constexpr int NUM_THREADS = (PRODUCER_WARP0 + NUM_PRODUCER_WARPS) * 32;
 static_assert(EPILOGUE_WARP0 % 4 == 0, "epilogue warps must start at a multiple of four");
 constexpr int64_t SPLIT256_OPERAND_BYTES = 8ll << 20;   // dense operand size above which width 256 runs as two 128-column passes
-constexpr int LONG_WINDOW_SHIFT = 4;                 // a cut inside a window of at most chunk >> 4 tiles moves to the window start
+// A cut of the tile array that falls inside a window of at most min(chunk / 2, LONG_WINDOW_TILES)
+// tiles moves back to the window's first tile: finishing a window that is split between two CTAs
+// costs about as much as 100 tiles of work (partial tiles through global memory, a counter, the
+// sum), so only windows well above that are worth splitting; the cap keeps the imbalance this
+// causes at a few per cent of a large CTA range.
+#ifndef GRWS_TC5_LW_TILES
+#define GRWS_TC5_LW_TILES 512
+#endif
+constexpr int64_t LONG_WINDOW_TILES = GRWS_TC5_LW_TILES;                 // a cut inside a window of at most chunk >> 4 tiles moves to the window start
 constexpr long long WAIT_LIMIT_CYCLES = 3000000000ll;   // default: a wait gives up after about 1.5-2.5 s of SM clocks
 
 // status codes: which wait ran out (the first four) / an injected failure of the self-test build
@@ -121,17 +129,27 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 }
 __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
+#ifdef GRWS_TC5_WAIT_HINT_NS
+    // the hint lets the hardware keep the thread suspended for up to that long before it reports failure
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity), "r"((uint32_t)GRWS_TC5_WAIT_HINT_NS) : "memory");
+#else
     asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
                  : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+#endif
     return ok;
 }
 // bounded wait: gives up after `limit` SM clocks or when another role already aborted.
 // (The SM clock is used because reading %globaltimer costs about a microsecond per read.)
+template <bool SLEEPY = false>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, long long limit) {
     if (mbar_try_wait(bar, parity)) return true;
     long long t0 = 0;
     for (uint32_t i = 0;; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
+#ifdef GRWS_TC5_SLEEP_NS
+        if (SLEEPY) __nanosleep(GRWS_TC5_SLEEP_NS);
+#endif
         if ((i & 63u) == 63u) {
             if (*abort_flag) return false;
             const long long now = clock64();
@@ -151,7 +169,6 @@ __device__ __forceinline__ bool mbar_wait_drain(uint32_t bar, uint32_t parity, l
 // wait that adds its duration to `acc` in the profiling build of the kernel
 template <bool PROF>
 __device__ __forceinline__ bool mbar_wait_t(uint32_t bar, uint32_t parity, volatile int *abort_flag, long long limit, long long &acc, int role = 0) {
-    (void)role;
     if constexpr (PROF) {
         // (a try_wait may itself suspend the thread until the phase completes, so even a wait whose
         // first try succeeds has to be timed)
@@ -161,7 +178,10 @@ __device__ __forceinline__ bool mbar_wait_t(uint32_t bar, uint32_t parity, volat
         return ok;
     } else {
         (void)acc;
-        return mbar_wait(bar, parity, abort_flag, limit);
+        // (experiment builds let the roles with slack -- a producer waiting for its slot, the
+        // epilogue, the walker -- sleep between polls)
+        if (role == 2 || role == 4 || role == 5) return mbar_wait<true>(bar, parity, abort_flag, limit);
+        return mbar_wait<false>(bar, parity, abort_flag, limit);
     }
 }
 // timeline of the first stages of CTA 0 (profiling build): event e of stage `it`
@@ -174,6 +194,16 @@ template <bool PROF> __device__ __forceinline__ void prof_mark(long long *dbg, u
 }
 template <bool PROF> __device__ __forceinline__ long long prof_clock() {
     if constexpr (PROF) return clock64(); else return 0;
+}
+// wall-clock timestamp (ns) of the profiling build: comparable across SMs
+template <bool PROF> __device__ __forceinline__ void prof_stamp(long long *dbg, int slot) {
+    if constexpr (PROF) {
+        if (dbg) {
+            unsigned long long t;
+            asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+            dbg[8192 + (size_t)blockIdx.x * 8 + slot] = (long long)t;
+        }
+    }
 }
 // clock reads inside the per-stage loops: only in the timeline build (they slow the loops down)
 template <bool PROF> __device__ __forceinline__ long long prof_fine() {
@@ -377,8 +407,14 @@ template <int NH> struct Cfg {
     static constexpr size_t kSmem = 1024 + sizeof(SharedStorage) + 16 + (size_t)kStages * kStageBytes + (size_t)kMeta * META_BYTES + kStagingBytes;
 };
 
+// The launch is a programmatic dependent of the small kernel that zeroes the status word and the
+// split-window counters: this kernel may start before that one has finished, and whoever is about
+// to touch those words waits for it here (a no-op when the launch was an ordinary one).
+__device__ __forceinline__ void wait_for_zeroed_scratch() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 __device__ __forceinline__ void raise(Params const &prm, SharedStorage *ss, int code) {
     ss->abort_flag = 1;
+    wait_for_zeroed_scratch();
     atomicMax(prm.status, code);
     if (prm.sticky) atomicMax(prm.sticky, code);
 }
@@ -463,6 +499,7 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
 #endif
     const int skip = PROF ? prm.skip : GRWS_TC5_BUILD_SKIP;   // folds to zero in the product kernel
     const long long limit = prm.wait_limit;
+    if (threadIdx.x == 0) prof_stamp<PROF>(prm.dbg, 0);           // kernel entry
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < C::kStages; ++i) { mbar_init(smem_u32(&ss->full_g[i]), 1); mbar_init(smem_u32(&ss->empty_g[i]), 1); }
@@ -482,6 +519,7 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
     tc_fence_after();
     const uint32_t tmem_base = ss->tmem_base;
     volatile int *abort_flag = &ss->abort_flag;
+    if (threadIdx.x == 0) prof_stamp<PROF>(prm.dbg, 1);           // barriers and tensor memory set up
 
     if (warp == WALK_WARP || (warp >= EPILOGUE_WARP0 && warp < MMA_WARP)) {
         // ---- the two roles that walk the window structure: this CTA's tile range [s, e)
@@ -490,13 +528,14 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
         int64_t chunk = (T + G - 1) / G;
         chunk = (chunk + 1) & ~int64_t(1);
         if (chunk < 2) chunk = 2;
-        // a cut inside a window of at most chunk/16 tiles moves back to that window's start, so
-        // only long windows are ever split between CTAs (tile counts stay balanced within chunk / 16)
-        const int64_t long_window = chunk >> LONG_WINDOW_SHIFT;
+        // a cut inside a short window moves back to that window's start: only long windows are
+        // ever split between CTAs
+        const int64_t long_window = min(chunk >> 1, LONG_WINDOW_TILES);
         int64_t w_first, s, e;
         warp_cut_pair(prm.window_offset, W, T, blockIdx.x, G, chunk, long_window, lane, &s, &e, &w_first);
         Walker wk;
         wk.init(prm.window_offset, W, s, e, blockIdx.x == 0 ? 0 : w_first, lane);
+        if (warp == WALK_WARP && lane == 0) prof_stamp<PROF>(prm.dbg, 2);     // tile range found
 
         if (warp == WALK_WARP) {
             // -------------------------------------------------------------- walker
@@ -553,10 +592,9 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
             long long w_af = 0;
             const long long t_epi0 = prof_clock<PROF>();
             // 16-bit outputs go through shared memory: every thread holds one feature of the 16 rows
-            // (a tensor-memory lane), the window's rows are assembled in `staging` and leave as one
-            // bulk store when the output rows are contiguous (ldc == N), else one per row
+            // (a tensor-memory lane), the window's rows are assembled in `staging` and leave as
+            // 16-byte vector stores, 256 contiguous bytes per 16 threads
             const bool staged = prm.c_dtype != GRWS_F32 && !(skip & SKIP_STORE);
-            const int64_t row_bytes = (int64_t)SLAB * NH * 2;
             // Windows without tiles produce zero rows.  They are dealt to all CTAs here, while the
             // pipeline fills, instead of being written by whichever CTA's tile range they border:
             // a run of empty windows (padded blocks, isolated nodes) would serialise on that one CTA.
@@ -570,15 +608,14 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
                 const uint32_t buf = ai % NACC, aph = (ai / NACC) & 1u;
                 ++ai;
                 // One thread polls for all four warps (threads spinning on a barrier slow every other
-                // barrier operation of the SM down); it also makes sure that the previous window's
-                // bulk store has finished reading `staging`.  All four warps then meet and leave
-                // together when the wait ran out or another role gave up: none may be left alone at a
-                // later barrier.
+                // barrier operation of the SM down).  All four warps then meet and leave together
+                // when the wait ran out or another role gave up: none may be left alone at a later
+                // barrier.  The barrier also orders the previous window's reads of `staging` before
+                // this window's writes.
                 bool ok = true;
                 if (threadIdx.x == EPILOGUE_WARP0 * 32) {
                     ok = mbar_wait_t<PROF>(smem_u32(&ss->acc_full[buf]), aph, abort_flag, limit, w_af, 4);
                     if (!ok) raise(prm, ss, ST_TIMEOUT_ACC);
-                    bulk_wait_read0();
                 }
                 if (epilogue_sync_or(!ok || *abort_flag != 0)) break;
                 tc_fence_after();
@@ -602,18 +639,20 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
                                                                          : __bfloat16_as_ushort(__float2bfloat16_rn(x));
                         }
                     }
-                    fence_async_smem();                    // the bulk store reads through the async proxy
                     epilogue_sync();
-                    if (threadIdx.x == EPILOGUE_WARP0 * 32) {
+                    // 16 threads per 256-byte row: whole rows leave as 16-byte vector stores.  (A bulk
+                    // store from shared memory would queue behind the gathers in the TMA unit and
+                    // hold the staging buffer, and with it the accumulators, for thousands of cycles.)
+                    {
+                        constexpr int CPR = SLAB * NH * 2 / 16;            // 16-byte pieces per row
                         char *dst = static_cast<char *>(prm.C) + (w * TILE_ROWS) * prm.ldc * 2;
-                        if (prm.ldc == prm.N) {
-                            bulk_s2g(dst, smem_u32(staging), (uint32_t)(TILE_ROWS * row_bytes), pol);
-                        } else {
-#pragma unroll 1
-                            for (int r = 0; r < TILE_ROWS; ++r)
-                                bulk_s2g(dst + (int64_t)r * prm.ldc * 2, smem_u32(staging) + (uint32_t)(r * row_bytes), (uint32_t)row_bytes, pol);
+#pragma unroll
+                        for (int c = threadIdx.x; c < TILE_ROWS * CPR; c += NUM_EPILOGUE) {
+                            const int r = c / CPR, k = c % CPR;
+                            const uint4 val = *reinterpret_cast<const uint4 *>(staging + r * (SLAB * NH * 2) + k * 16);
+                            asm volatile("st.global.L2::cache_hint.v4.b32 [%0], {%1, %2, %3, %4}, %5;"
+                                         ::"l"(dst + (int64_t)r * prm.ldc * 2 + k * 16), "r"(val.x), "r"(val.y), "r"(val.z), "r"(val.w), "l"(pol) : "memory");
                         }
-                        bulk_commit();
                     }
                 } else if (!partial) {
 #pragma unroll
@@ -635,19 +674,30 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
                     // the CTA that holds the window's first tile, and the one that arrives last sums the
                     // pieces in CTA order (the same order whoever is last) and writes the rows.  Cuts
                     // inside a split window are never moved, so its pieces are exactly the CTAs
-                    // a / chunk .. (b - 1) / chunk.
-                    __threadfence();
-                    epilogue_sync();
+                    // a / chunk .. (b - 1) / chunk.  A holder that finds all the others already counted
+                    // is the last one for sure and goes straight to the sum (its own piece was written by
+                    // the very threads that read it back: no fence, no atomic).
                     const int64_t k0 = wk.a / chunk, k_last = (wk.b - 1) / chunk;
                     if (threadIdx.x == EPILOGUE_WARP0 * 32) {
-                        const int old = atomicAdd(prm.split_count + k0, 1);
-                        ss->last_piece = (old == (int)(k_last - k0)) ? 1 : 0;
+                        wait_for_zeroed_scratch();
+                        int seen;
+                        asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(prm.split_count + k0) : "memory");
+                        ss->last_piece = (seen == (int)(k_last - k0)) ? 2 : 0;
                     }
                     epilogue_sync();
+                    if (*reinterpret_cast<volatile int *>(&ss->last_piece) != 2) {
+                        __threadfence();
+                        epilogue_sync();
+                        if (threadIdx.x == EPILOGUE_WARP0 * 32) {
+                            const int old = atomicAdd(prm.split_count + k0, 1);
+                            ss->last_piece = (old == (int)(k_last - k0)) ? 1 : 0;
+                        }
+                        epilogue_sync();
+                    }
                     if (*reinterpret_cast<volatile int *>(&ss->last_piece)) sum_pieces<NH>(prm.partial, prm.N, prm.C, prm.ldc, prm.c_dtype, w, k0, k_last, q, lane);
                 }
             }
-            if (threadIdx.x == EPILOGUE_WARP0 * 32) bulk_wait0();      // this CTA's output stores are complete
+            if (threadIdx.x == EPILOGUE_WARP0 * 32) prof_stamp<PROF>(prm.dbg, 5);      // last rows written
             if (PROF && prm.dbg && threadIdx.x == EPILOGUE_WARP0 * 32) { prm.dbg[blockIdx.x * 16 + 7] = w_af; prm.dbg[blockIdx.x * 16 + 14] = prof_clock<PROF>() - t_epi0; }
         }
     } else if (warp >= PRODUCER_WARP0) {
@@ -820,6 +870,7 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
                     // so this one wait also covers the tile values and the command word.
                     if (!mbar_wait_t<PROF>(smem_u32(&ss->full_g[gs]), gph, abort_flag, limit, w_fg, 1)) { raise(prm, ss, ST_TIMEOUT_FULL); stop = true; break; }
                     prof_mark<PROF>(prm.dbg, it, 5);
+                    if (it == 0) prof_stamp<PROF>(prm.dbg, 3);     // first stage ready for the MMAs
                     const uint32_t ms = (uint32_t)gs * D + nd;     // the stage's meta slot
                     const uint32_t cmd = *reinterpret_cast<const volatile uint32_t *>(ring_m + ms * META_BYTES + META_TILE_BYTES + META_COL_BYTES);
                     if (cmd & CMD_END) { stop = true; break; }
@@ -866,6 +917,7 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
                 gph ^= 1u;
                 if (++nd == D) nd = 0;
             }
+            prof_stamp<PROF>(prm.dbg, 4);                          // last MMA issued
             if (issued && *abort_flag) {
                 // aborted: tensor memory is freed below, so the MMAs still in the pipe must finish first
                 umma_commit(smem_u32(&ss->drain));
@@ -886,6 +938,7 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
         tc_fence_after();
         tmem_dealloc(tmem_base, C::kTmemCols);
     }
+    if (threadIdx.x == 0) prof_stamp<PROF>(prm.dbg, 6);           // CTA done
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -894,6 +947,7 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
 constexpr size_t STATUS_BYTES = 256;
 constexpr size_t DEBUG_BYTES = 1024 * 16 * sizeof(long long);   // profiling counters (unused by the product kernel, kept in the layout)
 constexpr size_t FIX_BYTES = 1024 * 4 * sizeof(int64_t);      // per-CTA counters of finished pieces of split windows
+constexpr int64_t MIN_TILES_PER_CTA = 64;
 constexpr int SCRATCH_CTAS_PER_SM = 4;                        // partial-tile slots are sized for up to this many CTAs per SM
 static_assert(GRWS_TC5_CTAS_PER_SM <= SCRATCH_CTAS_PER_SM, "scratch sizing");
 
@@ -954,12 +1008,39 @@ static int profile_env(const char *name) {
 }
 #endif
 
-template <int NH>
-static void launch_kernel(const Params &prm, const CUtensorMap &b_map, int G, cudaStream_t stream) {
-#ifdef GRWS_TC5_PROFILING
-    if (prm.dbg) { spmm_tc5_kernel<NH, true><<<G, NUM_THREADS, Cfg<NH>::kSmem, stream>>>(prm, b_map); return; }
+// Zeroes `n` 32-bit words (status word, split-window counters) and lets the SpMM kernel queued
+// behind it start at once: that kernel's set-up and first stages overlap this one, and it waits
+// (griddepcontrol.wait) only where it first touches these words.
+__global__ void zero_words_kernel(int *p, int n) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    for (int i = threadIdx.x; i < n; i += blockDim.x) p[i] = 0;
+}
+
+template <int NH, bool PROF>
+static cudaError_t launch_dependent(const Params &prm, const CUtensorMap &b_map, int G, cudaStream_t stream) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)G);
+    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.dynamicSmemBytes = Cfg<NH>::kSmem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+#ifdef GRWS_TC5_NO_PDL
+    cfg.numAttrs = 0;
+#else
+    cfg.numAttrs = 1;
 #endif
-    spmm_tc5_kernel<NH, false><<<G, NUM_THREADS, Cfg<NH>::kSmem, stream>>>(prm, b_map);
+    return cudaLaunchKernelEx(&cfg, spmm_tc5_kernel<NH, PROF>, prm, b_map);
+}
+
+template <int NH>
+static cudaError_t launch_kernel(const Params &prm, const CUtensorMap &b_map, int G, cudaStream_t stream) {
+#ifdef GRWS_TC5_PROFILING
+    if (prm.dbg) return launch_dependent<NH, true>(prm, b_map, G, stream);
+#endif
+    return launch_dependent<NH, false>(prm, b_map, G, stream);
 }
 
 // Tensor map of the dense operand for the row gathers: 2-D [K rows][N features], box of one row
@@ -1060,7 +1141,11 @@ int spmm_tc5_launch(const int64_t *window_offset, const int32_t *cols, const voi
     // launches).
     const bool split = N == 256 && K * 512 > SPLIT256_OPERAND_BYTES;
     const int64_t pass_n = (N == 128 || split) ? 128 : 256;
-    const int G = dev->sms * (pass_n == 128 ? Cfg<1>::kCtasPerSm : Cfg<2>::kCtasPerSm);
+    // one persistent CTA per SM slot, fewer for small products: a CTA range below ~64 tiles is mostly
+    // cuts through windows, whose pieces then cost more to put together than the tiles to multiply
+    int G = dev->sms * (pass_n == 128 ? Cfg<1>::kCtasPerSm : Cfg<2>::kCtasPerSm);
+    const int64_t g_small = num_tiles_bound / MIN_TILES_PER_CTA;
+    if (g_small < G) G = g_small < 1 ? 1 : (int)g_small;
     if ((size_t)G * sizeof(int) > FIX_BYTES) return fail(GRWS_ERR_UNSUPPORTED, "more CTAs (%d) than split-window counters", G);
     const size_t c_elem = c_dtype == GRWS_F32 ? 4 : 2;
     for (int64_t col0 = 0; col0 < N; col0 += pass_n) {
@@ -1070,10 +1155,10 @@ int spmm_tc5_launch(const int64_t *window_offset, const int32_t *cols, const voi
         alignas(64) CUtensorMap b_map;
         if (int st = encode_b_map(&b_map, prm.B, prm.is_bf16, K, pass_n, ldb)) return st;
         // the status word is cleared once per call, the split-window counters before every pass
-        if (col0 == 0) GRWS_CUDA_TRY(cudaMemsetAsync(scratch, 0, STATUS_BYTES + sizeof(int) * (size_t)G, stream));
-        else GRWS_CUDA_TRY(cudaMemsetAsync(prm.split_count, 0, sizeof(int) * (size_t)G, stream));
-        if (pass_n == 128) launch_kernel<1>(prm, b_map, G, stream);
-        else launch_kernel<2>(prm, b_map, G, stream);
+        if (col0 == 0) zero_words_kernel<<<1, 256, 0, stream>>>(static_cast<int *>(scratch), (int)(STATUS_BYTES / sizeof(int)) + G);
+        else zero_words_kernel<<<1, 256, 0, stream>>>(prm.split_count, G);
+        GRWS_CUDA_TRY(cudaGetLastError());
+        GRWS_CUDA_TRY((pass_n == 128 ? launch_kernel<1>(prm, b_map, G, stream) : launch_kernel<2>(prm, b_map, G, stream)));
         GRWS_CUDA_TRY(cudaGetLastError());
     }
     return GRWS_OK;
