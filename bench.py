@@ -614,11 +614,13 @@ def secondary_gcn_full(args, torch, scale=1.0, steps=10):
     y = torch.randint(0, 41, (n,), generator=gen, device=device)
     train = torch.randperm(n, generator=gen, device=device)[:n // 2].sort().values
     model = GCN_BCSR(608, 256, 41, num_layers=2, dropout=0.5, use_checkpoint=False).to(device).bfloat16()
-    opt = torch.optim.Adam(model.parameters(), lr=1e-3, eps=1e-4)
+    opt = torch.optim.Adam(model.parameters(), lr=1e-3, eps=1e-4, capturable=not args.eager)
     tiles = int(graph.window_offset[-1])
+    step_args = None
     if world == 1:
         graph.transposed(n, dtype=torch.bfloat16)
         step = lambda: train_step_full(model, graph, x, y, train, opt)   # noqa: E731
+        step_args = (model, graph, x, y, train, opt, None)
     else:
         for p_ in model.parameters():
             dist.broadcast(p_.data, 0)
@@ -631,9 +633,30 @@ def secondary_gcn_full(args, torch, scale=1.0, steps=10):
         del graph, x, y
         torch.cuda.empty_cache()
         step = lambda: train_step_full_sharded(model, shard, x_l, y_l, mine, n_train, opt)   # noqa: E731
+        step_args = (model, shard, x_l, y_l, mine, opt, n_train)
     for _ in range(3):
         step()
     barrier()
+    eager_step, step_mode = step, "eager"
+    if not args.eager:
+        # the epoch as one CUDA graph (collectives included): at eight ranks an epoch is ~2 ms of GPU
+        # time and about as much interpreter time to issue
+        try:
+            from graph_rws_b200.helper import graphed_full_step
+            m_, g_, x_, y_, t_, o_, nt_ = step_args
+            step = graphed_full_step(m_, g_, x_, y_, t_, o_, num_train=nt_)
+            step_mode = "cuda graph"
+        except Exception as exc:          # noqa: BLE001
+            sys.stderr.write(f"bench.py: gcn_full epoch not captured ({exc}); eager loop\n")
+            step = eager_step
+        if world > 1:                     # every rank must take the same path through the collectives
+            flag = torch.tensor([1 if step_mode == "cuda graph" else 0], device=device)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            if int(flag) == 0:
+                step, step_mode = eager_step, "eager"
+        for _ in range(2):
+            step()
+        barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t_host0 = time.perf_counter()
     e0.record()
@@ -647,7 +670,7 @@ def secondary_gcn_full(args, torch, scale=1.0, steps=10):
     # the read-out serialise a little)
     collective_timers.start()
     for _ in range(3):
-        step()
+        eager_step()
     torch.cuda.synchronize()
     coll = collective_timers.stop()
     ms = torch.tensor([e0.elapsed_time(e1) / steps, coll.get("all_gather", 0.0) / 3, coll.get("all_reduce", 0.0) / 3],
@@ -657,6 +680,7 @@ def secondary_gcn_full(args, torch, scale=1.0, steps=10):
     out = {"metric": "GCN epoch ms (full-graph 2-layer, row-partitioned)", "ms": float(ms[0]), "n": world, "scaling": "strong",
            "scale": scale, "nodes": n, "nnz": nnz, "tiles": tiles, "features": 602, "hidden": 256, "classes": 41, "dtype": "bf16",
            "all_gather_ms_per_epoch": float(ms[1]), "all_reduce_ms_per_epoch": float(ms[2]), "host_issue_ms_per_epoch": host_ms,
+           "step_mode": step_mode,
            "parallelism": "rows x%d, all-gather of H / dY per layer, all-reduce of weight gradients" % world}
     del model, opt
     torch.cuda.empty_cache()
@@ -703,7 +727,7 @@ def secondary_sampled(args, torch, scale=1.0, steps=10):
     if world > 1:
         for p_ in model.parameters():
             dist.broadcast(p_.data, 0)
-    opt = torch.optim.Adam(model.parameters(), lr=1e-3, eps=1e-4)
+    opt = torch.optim.Adam(model.parameters(), lr=1e-3, eps=1e-4, capturable=not args.eager)
     sampler = BCSRSampler([15, 10, 5], verbose=False, pad_to=256)          # fused: one call per step, no read-backs
     per_gpu = 1024
     state = {"i": 0}
@@ -728,6 +752,27 @@ def secondary_sampled(args, torch, scale=1.0, steps=10):
     for _ in range(3):
         step()
     barrier()
+    step_mode = "eager"
+    if not args.eager and (fetch is None or hasattr(fetch, "gather")):
+        # the whole step as one CUDA graph: a few hundred small kernels take longer to issue from the
+        # interpreter than to run (the all-to-all feature exchange reads sizes back and cannot be captured)
+        eager_step = step
+        try:
+            from graph_rws_b200.helper import graphed_sampled_step
+            gstep = graphed_sampled_step(model, sampler, topo, x_local, y, opt, per_gpu, fetch_rows=fetch)
+            step = lambda: gstep(seeds_for_step(), state["i"])   # noqa: E731
+            step_mode = "cuda graph"
+        except Exception as exc:          # noqa: BLE001
+            sys.stderr.write(f"bench.py: sampled step not captured ({exc}); eager loop\n")
+            step = eager_step
+        if world > 1:
+            flag = torch.tensor([1 if step_mode == "cuda graph" else 0], device=device)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            if int(flag) == 0:
+                step, step_mode = eager_step, "eager"
+        for _ in range(2):
+            step()
+        barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(steps):
@@ -761,7 +806,7 @@ def secondary_sampled(args, torch, scale=1.0, steps=10):
     peak, peak_kind = measured_peaks()
     achieved = sb["total"] / (samp_ms * 1e-3) / 1e9
     out = {"metric": "sampled seeds/s (sample + build + 3-layer GCN step)", "seeds_per_s": world * per_gpu / (step_ms * 1e-3),
-           "ms_per_step": step_ms, "sampling_only_seeds_per_s": world * per_gpu / (samp_ms * 1e-3), "sampling_ms": samp_ms,
+           "ms_per_step": step_ms, "step_mode": step_mode, "sampling_only_seeds_per_s": world * per_gpu / (samp_ms * 1e-3), "sampling_ms": samp_ms,
            "n": world, "scaling": "weak", "scale": scale, "nodes": n, "nnz": nnz, "fanouts": [15, 10, 5], "seeds_per_gpu": per_gpu,
            "hidden": 256, "dtype": "f16", "topology": "CSR replicated per GPU, no full-graph BCSR",
            "features": feature_path,

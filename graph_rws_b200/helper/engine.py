@@ -155,6 +155,90 @@ def train_step_sampled(model, sampler, graph, features, labels, seeds, optimizer
     return loss.detach()
 
 
+class GraphedStep:
+    """A training step captured once as a CUDA graph and replayed: the whole step -- sampling, block
+    build, forward, backward, gradient all-reduce, clipping, optimizer -- becomes one graph launch.
+
+    A sampled step queues a few hundred small kernels; issued one by one from the interpreter they
+    take longer to issue than to run.  Everything in the step has fixed shapes (the fused sampler
+    sizes its blocks by bounds) and reads what changes from step to step -- the seeds, the Philox
+    seed -- from device buffers, so the recorded launch sequence is valid for every step.
+
+    ``body()`` runs one step on static inputs and returns the loss tensor; the optimizer must be
+    capturable (``torch.optim.Adam(..., capturable=True)``).  The first calls run eagerly on a
+    side stream (libraries pick their algorithms, the allocator warms up, this library looks up
+    its device symbols), then the body is captured."""
+
+    def __init__(self, body, device, warmup: int = 3):
+        self.body = body
+        side = torch.cuda.Stream(device)
+        side.wait_stream(torch.cuda.current_stream(device))
+        with torch.cuda.stream(side):
+            for _ in range(warmup):
+                body()
+        torch.cuda.current_stream(device).wait_stream(side)
+        torch.cuda.synchronize(device)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.loss = body()
+
+    def replay(self):
+        self.graph.replay()
+        return self.loss
+
+
+def graphed_sampled_step(model, sampler, graph, features, labels, optimizer, num_seeds, fetch_rows=None, warmup=3):
+    """``step(seeds, step_index) -> loss`` for sampled training, as one CUDA graph per step."""
+    device = labels.device
+    seeds_buf = torch.zeros(num_seeds, dtype=torch.int32, device=device)
+    seed_dev = torch.zeros(1, dtype=torch.int64, device=device)          # the Philox seed, read by the sampling kernels
+
+    def body():
+        blocks, x = layer0_inputs(sampler.sample_layers(graph, seeds_buf, seed_dev=seed_dev), features, fetch_rows)
+        _zero_grads(model, optimizer)
+        logits = model(blocks, x)[:num_seeds]
+        loss = F.cross_entropy(logits.float(), labels[seeds_buf.long()])
+        loss.backward()
+        _allreduce_grads(model)
+        torch.nn.utils.clip_grad_norm_(model.parameters(), max_norm=1.0)
+        optimizer.step()
+        return loss.detach()
+
+    model.train()
+    graphed = GraphedStep(body, device, warmup)
+
+    def step(seeds, step_index=0):
+        seeds_buf.copy_(seeds, non_blocking=True)
+        seed_dev.fill_(int(sampler.seed) + int(step_index))
+        return graphed.replay()
+    step.graphed = graphed
+    return step
+
+
+def graphed_full_step(model, graph, features, labels, train_idx, optimizer, num_train=None, warmup=3):
+    """``step() -> loss`` for full-graph training (one GPU, or a row shard with ``num_train`` = the
+    global number of training rows) as one CUDA graph per epoch."""
+    device = labels.device
+    sharded = num_train is not None
+
+    def body():
+        _zero_grads(model, optimizer)
+        logits = model(graph, features)
+        if sharded:
+            loss = F.cross_entropy(logits[train_idx].float(), labels[train_idx], reduction='sum') / num_train
+        else:
+            loss = F.cross_entropy(logits[train_idx].float(), labels[train_idx])
+        loss.backward()
+        _allreduce_grads(model, average=not sharded)
+        torch.nn.utils.clip_grad_norm_(model.parameters(), max_norm=1.0)
+        optimizer.step()
+        return loss.detach()
+
+    model.train()
+    graphed = GraphedStep(body, device, warmup)
+    return graphed.replay
+
+
 def _record_stream(obj, stream):
     """Tell the caching allocator that ``stream`` uses the tensors of ``obj`` (a tensor, a block or a
     list of them), which were allocated on another stream."""
