@@ -46,5 +46,25 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
+SELFTEST_LIB = os.path.join(HERE, "libgrws_b200_selftest.so")
+
+
+def build_selftest(force: bool = False) -> str:
+    """The same library with the SpMM kernel's profiling build compiled in (-DGRWS_TC5_PROFILING):
+    per-role wait counters, and the switch the time-out self-test uses to withhold one barrier
+    arrive.  Only spmm_tcgen05.cu is compiled again; the other objects are the product's."""
+    build()
+    src = os.path.join(HERE, "spmm_tcgen05.cu")
+    if not force and os.path.exists(SELFTEST_LIB) and os.path.getmtime(SELFTEST_LIB) >= os.path.getmtime(LIB):
+        return SELFTEST_LIB
+    obj = os.path.join(HERE, "build", "spmm_tcgen05.selftest.o")
+    subprocess.check_call([NVCC] + FLAGS + ["-DGRWS_TC5_PROFILING", "-c", src, "-o", obj])
+    objs = [os.path.join(HERE, "build", os.path.basename(s) + ".o") for s in sources() if s != src] + [obj]
+    subprocess.check_call([NVCC, "-shared", "-o", SELFTEST_LIB] + objs + ["-lcudart", "-ccbin", "/usr/bin/g++"])
+    return SELFTEST_LIB
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    if "--selftest" in sys.argv:
+        print(build_selftest(force="--force" in sys.argv))
