@@ -168,6 +168,28 @@ def algorithmic_bytes(graph, rows_touched, width, esize, torch):
     return synthetic.spmm_algorithmic_bytes(graph.num_windows, T, rows_touched, width, esize, esize, esize)
 
 
+def same_graph_on_every_rank(rp, ci, vv, torch, world, rank):
+    """Every rank draws the synthetic graph from the same seed; the draws are compared and, should a
+    device have produced another graph (library kernels are not bit-reproducible across every
+    configuration), rank 0's arrays are broadcast so that all ranks hold one graph."""
+    if world == 1:
+        return rp, ci, vv
+    import torch.distributed as dist
+    chk = torch.stack([ci.long().sum(), -ci.long().sum(), torch.tensor(ci.numel(), device=ci.device), -torch.tensor(ci.numel(), device=ci.device)])
+    dist.all_reduce(chk, op=dist.ReduceOp.MAX)
+    if int(chk[0]) == -int(chk[1]) and int(chk[2]) == -int(chk[3]):
+        return rp, ci, vv
+    nnz = torch.tensor([ci.numel()], device=ci.device)
+    dist.broadcast(nnz, 0)
+    if rank != 0:
+        ci = torch.empty(int(nnz), dtype=ci.dtype, device=ci.device)
+        vv = torch.empty(int(nnz), dtype=vv.dtype, device=vv.device)
+    dist.broadcast(rp, 0)
+    dist.broadcast(ci, 0)
+    dist.broadcast(vv, 0)
+    return rp, ci, vv
+
+
 def dist_env(torch):
     import torch.distributed as dist
     rank = int(os.environ.get("RANK", "0"))
@@ -176,7 +198,10 @@ def dist_env(torch):
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
     if world > 1 and not dist.is_initialized():
-        dist.init_process_group("nccl", device_id=device)
+        import datetime
+        # a collective that does not complete ends the run with an error after three minutes
+        # instead of occupying the GPUs until somebody kills the job
+        dist.init_process_group("nccl", device_id=device, timeout=datetime.timedelta(seconds=180))
 
     def barrier():
         if world > 1:
@@ -601,10 +626,7 @@ def secondary_gcn_full(args, torch, scale=1.0, steps=10):
     n = int(232965 * scale)
     e = int((114_600_000 * scale * scale - n) // 2)
     rp, ci, vv = synthetic.community_csr_torch(n, e, 50, 0.8, 1003, device)
-    if world > 1:      # every rank draws the graph itself: the draws must agree
-        chk = torch.stack([ci.long().sum(), -ci.long().sum()])
-        dist.all_reduce(chk, op=dist.ReduceOp.MAX)
-        assert int(chk[0]) == -int(chk[1]), "ranks drew different graphs"
+    rp, ci, vv = same_graph_on_every_rank(rp, ci, vv, torch, world, rank)
     nnz = int(ci.numel())
     graph = BCSRGraph.from_csr(n, rp, ci, vv, device=device, values_dtype=torch.bfloat16)
     del rp, ci, vv
@@ -706,10 +728,7 @@ def secondary_sampled(args, torch, scale=1.0, steps=10):
     torch.manual_seed(1234)
     n, e = int(2449029 * scale), int(61_860_000 * scale)
     rp, ci, vv = synthetic.chung_lu_csr_torch(n, e, 2.5, 1004, device)
-    if world > 1:
-        chk = torch.stack([ci.long().sum(), -ci.long().sum()])
-        dist.all_reduce(chk, op=dist.ReduceOp.MAX)
-        assert int(chk[0]) == -int(chk[1]), "ranks drew different graphs"
+    rp, ci, vv = same_graph_on_every_rank(rp, ci, vv, torch, world, rank)
     topo = CSRTopology(rp, ci, vv, device=device, block_dtype=torch.float16)
     nnz = topo.nnz
     gen = torch.Generator(device=device).manual_seed(7)

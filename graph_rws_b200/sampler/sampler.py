@@ -12,8 +12,9 @@ blocks through its target-first slicing path; the features to pass are ``X[block
 and the logits rows line up with the seeds.  Edge values are the graph's own weights (the
 reference does not renormalise sampled blocks either).
 
-The importance-score options (HACS, locality bonus; sampler.py:101-153) and the partition
-samplers (sampler.py:307-756) are not part of this library.
+The importance-score options (HACS, locality bonus; sampler.py:101-153) are not part of this
+library.  The partition samplers (sampler.py:307-756: ``sample_partitions``, ``repack_subgraph``,
+``sample_dps_online``) keep their signatures and the attributes of what they return.
 """
 from typing import List
 
@@ -145,5 +146,144 @@ class BCSRSampler:
             print(f"  layer {layer_id}: sample {s['p1_sample'] / c:8.3f} ms  dedup/reindex {s['p2_map'] / c:8.3f} ms  "
                   f"block build {s['p3_recomp'] / c:8.3f} ms  total {s['total'] / c:8.3f} ms")
 
-    def sample_partitions(self, *args, **kwargs):
-        raise NotImplementedError("partition samplers are outside this library's scope")
+    # ------------------------------------------------------------------ partition samplers
+    # The reference's two partition-based mini-batch modes (sampler/sampler.py:307-756): a batch is
+    # a set of whole 16-row windows of the full graph, taken with all their tiles, the column ids
+    # relabelled to the batch's own node list.  Written here as a handful of device-wide tensor
+    # operations (window -> tile ranges by a segmented arange, relabelling through one lookup
+    # table) instead of per-partition host loops.
+
+    def _gather_windows(self, g: BCSRGraph, window_ids: torch.Tensor):
+        """Tiles of the given windows, in order: (new window_offset, cols [T, 8], vals [T, 16, 8] or None)."""
+        dev = window_ids.device
+
+        def at(src, idx):           # the graph's arrays may live in pinned host memory
+            return src[idx.to(src.device)].to(dev) if src.device != idx.device else src[idx]
+        starts, ends = at(g.window_offset, window_ids), at(g.window_offset, window_ids + 1)
+        lengths = ends - starts
+        new_wo = torch.zeros(window_ids.numel() + 1, dtype=torch.int64, device=dev)
+        torch.cumsum(lengths, 0, out=new_wo[1:])
+        total = int(new_wo[-1])                                   # the one size read-back of a batch
+        owner = torch.repeat_interleave(torch.arange(window_ids.numel(), device=dev), lengths, output_size=total)
+        tile_idx = starts[owner] + (torch.arange(total, device=dev) - new_wo[owner])
+        cols = at(g.original_col_indices.view(-1, self.tile_cols), tile_idx)
+        vals = None
+        if g.values_condensed is not None:
+            vals = at(g.values_condensed.view(-1, self.tile_rows, self.tile_cols), tile_idx)
+        return new_wo, cols, vals
+
+    def sample_partitions(self, g: BCSRGraph, partition_ids: torch.Tensor) -> BCSRGraph:
+        """The sub-BCSR induced by whole partitions of ``partition_book`` (entries with ``start_idx`` /
+        ``end_idx`` node ranges on window boundaries): rows and columns are the partitions' nodes,
+        numbered in the order the partitions are given; edges that leave the selection keep a -1
+        column id and contribute nothing (sampler/sampler.py:307-410)."""
+        if self.partition_book is None:
+            raise ValueError("Partition book is missing! Please set sampler.partition_book.")
+        dev = partition_ids.device
+        parts = [self.partition_book[int(p)] for p in partition_ids.tolist()]
+        lo = torch.tensor([p['start_idx'] for p in parts], dtype=torch.int64, device=dev)
+        hi = torch.tensor([p['end_idx'] for p in parts], dtype=torch.int64, device=dev)
+        sizes = hi - lo
+        first_local = torch.cumsum(sizes, 0) - sizes
+        n_local = int(sizes.sum())
+        part_of = torch.repeat_interleave(torch.arange(len(parts), device=dev), sizes, output_size=n_local)
+        nodes = lo[part_of] + (torch.arange(n_local, device=dev) - first_local[part_of])        # global id of local node i
+        node_map = torch.full((g.num_nodes,), -1, dtype=torch.int32, device=dev)
+        node_map[nodes] = torch.arange(n_local, dtype=torch.int32, device=dev)
+        w_lo, w_hi = lo // self.tile_rows, hi // self.tile_rows
+        w_sizes = w_hi - w_lo
+        w_first = torch.cumsum(w_sizes, 0) - w_sizes
+        n_win = int(w_sizes.sum())
+        wp = torch.repeat_interleave(torch.arange(len(parts), device=dev), w_sizes, output_size=n_win)
+        window_ids = w_lo[wp] + (torch.arange(n_win, device=dev) - w_first[wp])
+        new_wo, cols, vals = self._gather_windows(g, window_ids)
+        valid = (cols >= 0) & (cols < g.num_nodes)
+        local = torch.where(valid, node_map[cols.clamp(0, g.num_nodes - 1).long()], torch.full_like(cols, -1))
+        if vals is not None:
+            vals = vals.clone()
+            vals.masked_fill_((local < 0).unsqueeze(1), 0.0)
+        sub = BCSRGraph.from_components(new_wo, local.reshape(-1).contiguous(),
+                                        vals.reshape(-1) if vals is not None else None, num_rows=n_local,
+                                        num_cols=n_local, tile_rows=self.tile_rows, tile_cols=self.tile_cols, device=dev)
+        sub.active_windows = torch.arange(n_win, device=dev, dtype=torch.int32)
+        sub.is_local_input = True
+        return sub
+
+    def repack_subgraph(self, g: BCSRGraph, window_ids: torch.Tensor, max_external_ratio: float = 5.0,
+                        dry_run: bool = False):
+        """Halo-aware batch: the rows are the nodes of ``window_ids`` ("internal"), the columns are the
+        internal nodes followed by the neighbours outside them ("halo", at most
+        ``max_external_ratio`` x internal, a random subset beyond that); ``inner_graph`` is the same
+        block with the halo edges masked, for the layers after the first
+        (sampler/sampler.py:413-690)."""
+        from types import SimpleNamespace
+        dev = window_ids.device
+        window_ids = torch.sort(window_ids).values
+        window_ids = window_ids[(window_ids >= 0) & (window_ids < g.num_windows)]
+        R = self.tile_rows
+        if dry_run:                                               # sizes only, nothing is gathered
+            wo = g.window_offset
+            idx = window_ids.to(wo.device)
+            total_tiles = int((wo[idx + 1] - wo[idx]).sum()) if idx.numel() else 0
+            return SimpleNamespace(original_window_ids=window_ids, num_internal_nodes=window_ids.numel() * R,
+                                   total_tiles=total_tiles, approx_values=total_tiles * R * self.tile_cols,
+                                   approx_cols=total_tiles * self.tile_cols, values_condensed=None,
+                                   original_col_indices=None)
+        new_wo, cols, vals = self._gather_windows(g, window_ids)
+        internal = (window_ids.unsqueeze(1) * R + torch.arange(R, device=dev).unsqueeze(0)).reshape(-1)
+        internal = internal[internal < g.num_nodes]
+        n_int = int(internal.numel())
+        lookup = torch.full((g.num_nodes,), -1, dtype=torch.int32, device=dev)       # global id -> local id
+        lookup[internal] = torch.arange(n_int, dtype=torch.int32, device=dev)
+        valid = (cols >= 0) & (cols < g.num_nodes)
+        safe = cols.clamp(0, max(g.num_nodes - 1, 0)).long()
+        outside = valid & (lookup[safe] < 0)
+        halo = torch.unique(cols[outside].long())                 # ascending
+        budget = int(n_int * max_external_ratio)
+        if halo.numel() > budget:                                 # the out-of-memory guard of the reference
+            halo = torch.sort(halo[torch.randperm(halo.numel(), device=dev)[:budget]]).values
+        lookup[halo] = torch.arange(n_int, n_int + halo.numel(), dtype=torch.int32, device=dev)
+        input_nodes = torch.cat([internal, halo])
+        local = torch.where(valid, lookup[safe], torch.full_like(cols, -1))
+        if vals is not None:
+            vals = vals.clone()
+            vals.masked_fill_((local < 0).unsqueeze(1), 0.0)
+            vals.nan_to_num_(0.0)
+        sub = BCSRGraph.from_components(new_wo, local.reshape(-1).contiguous(),
+                                        vals.reshape(-1) if vals is not None else None, num_rows=n_int,
+                                        num_cols=int(input_nodes.numel()), tile_rows=R, tile_cols=self.tile_cols, device=dev)
+        sub.original_node_ids = input_nodes
+        sub.original_window_ids = window_ids
+        sub.is_local_input = True
+        sub.num_internal_nodes = n_int
+        inner_cols = torch.where(local >= n_int, torch.full_like(local, -1), local)
+        inner_vals = None
+        if vals is not None:
+            inner_vals = vals.clone()
+            inner_vals.masked_fill_((inner_cols < 0).unsqueeze(1), 0.0)
+        sub.inner_graph = BCSRGraph.from_components(new_wo, inner_cols.reshape(-1).contiguous(),
+                                                    inner_vals.reshape(-1) if inner_vals is not None else None,
+                                                    num_rows=n_int, num_cols=n_int, tile_rows=R,
+                                                    tile_cols=self.tile_cols, device=dev)
+        return sub
+
+    def sample_dps_online(self, g: BCSRGraph, seed_window_ids: torch.Tensor, fanouts: List[int] = [5, 5],
+                          dry_run: bool = False):
+        """Probe + repack (sampler/sampler.py:693-756): sample from the nodes of the seed windows,
+        take every window the sampled hops touch, and repack those windows as one halo-aware batch."""
+        dev = seed_window_ids.device
+        R = self.tile_rows
+        seeds = (seed_window_ids.unsqueeze(1) * R + torch.arange(R, device=dev).unsqueeze(0)).reshape(-1)
+        seeds = seeds[seeds < g.num_nodes]
+        if seeds.numel() == 0:
+            return self.repack_subgraph(g, torch.empty(0, dtype=torch.long, device=dev), dry_run=dry_run)
+        probe = BCSRSampler(fanouts, self.tile_rows, self.tile_cols, self.warps_per_block, verbose=False,
+                            seed=self.seed, fused=True)
+        probe.step = self.step
+        touched = [seed_window_ids.to(torch.int64)]
+        for block in probe.sample_layers(g, seeds):
+            ids = block.input_nodes
+            touched.append(torch.div(ids[ids >= 0], R, rounding_mode='floor').to(torch.int64))
+        windows = torch.unique(torch.cat(touched))
+        windows = windows[(windows >= 0) & (windows < g.num_windows)]
+        return self.repack_subgraph(g, windows, dry_run=dry_run)
