@@ -300,9 +300,16 @@ def run_ours(args):
     tc5 = args.algo != "warp" and dt in ("f16", "bf16") and width in (128, 256)
     launches_per_step = 2 * ((2 if (width == 256 and csr.num_nodes * 512 > (8 << 20)) else 1) if tc5 else 2)
 
+    # tile ranges of the CTAs: computed once per graph (what the layers do from the second product of
+    # a graph on), or searched by every launch (--no-plan)
+    plan_f = plan_t = None
+    if tc5 and not args.no_plan:
+        plan_f = core.spmm_plan(graph.window_offset, n_tiles, H.shape[0], width)
+        plan_t = core.spmm_plan(graph_t.window_offset, int(graph_t.original_col_indices.numel() // 8), G.shape[0], width)
+
     def step():
-        c = core.spmm_raw(graph.window_offset, graph.original_col_indices, graph.values_condensed, H)
-        d = core.spmm_raw(graph_t.window_offset, graph_t.original_col_indices, graph_t.values_condensed, G)
+        c = core.spmm_raw(graph.window_offset, graph.original_col_indices, graph.values_condensed, H, plan=plan_f)
+        d = core.spmm_raw(graph_t.window_offset, graph_t.original_col_indices, graph_t.values_condensed, G, plan=plan_t)
         return c, d
 
     sampler = ClockSampler(local_rank)
@@ -358,9 +365,9 @@ def run_ours(args):
     fwd_ms = []
     for _ in range(max(args.steps, 5)):
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        core.spmm_raw(graph_t.window_offset, graph_t.original_col_indices, graph_t.values_condensed, G)  # evicts H/C
+        core.spmm_raw(graph_t.window_offset, graph_t.original_col_indices, graph_t.values_condensed, G, plan=plan_t)  # evicts H/C
         a.record()
-        core.spmm_raw(graph.window_offset, graph.original_col_indices, graph.values_condensed, H)
+        core.spmm_raw(graph.window_offset, graph.original_col_indices, graph.values_condensed, H, plan=plan_f)
         b.record()
         b.synchronize()
         fwd_ms.append(a.elapsed_time(b))
@@ -454,6 +461,7 @@ def run_ours(args):
                     "d2h_bytes_per_step": int((csr.num_nodes + (csr.num_nodes + 15) // 16 * 16) * width) * esize,
                     "overlap": "forward and transposed chains on two streams: uploads and read-backs of neighbouring steps overlap"},
             "gpu_launches": launches_per_step * args.steps,
+            "tile_ranges": "planned once per graph, balanced by pipeline stages" if plan_f is not None else "searched by every launch",
             "timed_region": "CUDA graph replay of one step (two SpMM kernels + their memsets), K replays" if graph_step is not None
                             else "eager loop of K steps",
             "clocks": clocks,
@@ -899,6 +907,7 @@ def main():
     ap.add_argument("--algo", default="auto", choices=["auto", "warp", "tcgen05"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-secondary", action="store_true", help="SpMM line only")
+    ap.add_argument("--no-plan", action="store_true", help="every SpMM launch searches its tile ranges (no per-graph plan)")
     ap.add_argument("--no-ref-gpu", action="store_true")
     ap.add_argument("--eager", action="store_true", help="time an eager loop of steps instead of CUDA-graph replays")
     args = ap.parse_args()

@@ -64,10 +64,25 @@ def _scratch(nbytes: int, device):
     return torch.empty(max(int(nbytes), 16), dtype=torch.uint8, device=device)
 
 
-def spmm_raw(window_offset, cols, vals, B, out_dtype=None, algo=None, num_tiles_bound=None, check=False):
+def spmm_plan(window_offset, num_tiles, K, N):
+    """Tile ranges of the tcgen05 kernel's CTAs for one graph, balanced by pipeline stages, as a
+    uint8 CUDA tensor to pass to ``spmm_raw(plan=...)``.  Worth building for a graph that is
+    multiplied many times; it has to be rebuilt when ``window_offset`` changes.  No host
+    synchronisation."""
+    lib = _native.lib()
+    W = window_offset.shape[0] - 1
+    nbytes = lib.grws_spmm_plan_bytes(W, int(num_tiles), int(K), int(N))
+    plan = torch.empty(max(int(nbytes), 16), dtype=torch.uint8, device=window_offset.device)
+    _native.check(lib.grws_spmm_plan_build(_ptr(window_offset), W, int(num_tiles), int(K), int(N),
+                                           plan.data_ptr(), plan.numel(), _stream(window_offset.device)))
+    return plan
+
+
+def spmm_raw(window_offset, cols, vals, B, out_dtype=None, algo=None, num_tiles_bound=None, check=False, plan=None):
     """C[W*16, N] = A_bcsr @ B with values already in B's dtype and N % 8 == 0.
 
-    ``check=True`` synchronises and raises if a tcgen05 launch reported a timed-out wait."""
+    ``check=True`` synchronises and raises if a tcgen05 launch reported a timed-out wait;
+    ``plan`` is the result of ``spmm_plan`` for this graph, K and N (optional)."""
     lib = _native.lib()
     W = window_offset.shape[0] - 1
     K, N = B.shape
@@ -79,10 +94,16 @@ def spmm_raw(window_offset, cols, vals, B, out_dtype=None, algo=None, num_tiles_
     algo = _default_algo if algo is None else algo
     nbytes = lib.grws_spmm_scratch_bytes(W, T, N, algo)
     scratch = _scratch(nbytes, B.device)
-    _native.check(lib.grws_spmm_fwd(
-        _ptr(window_offset), _ptr(cols), _ptr(vals), _DT[vals.dtype], _ptr(B), _DT[B.dtype], B.stride(0),
-        C.data_ptr(), _DT[out_dtype], N, W, T, K, N, scratch.data_ptr(), scratch.numel(), algo,
-        _stream(B.device)))
+    if plan is not None:
+        _native.check(lib.grws_spmm_fwd_planned(
+            _ptr(window_offset), _ptr(cols), _ptr(vals), _DT[vals.dtype], _ptr(B), _DT[B.dtype], B.stride(0),
+            C.data_ptr(), _DT[out_dtype], N, W, T, K, N, scratch.data_ptr(), scratch.numel(), algo,
+            plan.data_ptr(), plan.numel(), _stream(B.device)))
+    else:
+        _native.check(lib.grws_spmm_fwd(
+            _ptr(window_offset), _ptr(cols), _ptr(vals), _DT[vals.dtype], _ptr(B), _DT[B.dtype], B.stride(0),
+            C.data_ptr(), _DT[out_dtype], N, W, T, K, N, scratch.data_ptr(), scratch.numel(), algo,
+            _stream(B.device)))
     if check:
         check_device_status(B.device)
     return C

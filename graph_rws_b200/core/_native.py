@@ -24,6 +24,10 @@ SIGNATURES = {
     "grws_spmm_resolve_algo": (c_i32, [c_i32, c_i64, c_i32]),
     "grws_spmm_fwd": (c_i32, [c_vp, c_vp, c_vp, c_i32, c_vp, c_i32, c_i64, c_vp, c_i32, c_i64,
                               c_i64, c_i64, c_i64, c_i64, c_vp, c_sz, c_i32, c_vp]),
+    "grws_spmm_plan_bytes": (c_sz, [c_i64, c_i64, c_i64, c_i64]),
+    "grws_spmm_plan_build": (c_i32, [c_vp, c_i64, c_i64, c_i64, c_i64, c_vp, c_sz, c_vp]),
+    "grws_spmm_fwd_planned": (c_i32, [c_vp, c_vp, c_vp, c_i32, c_vp, c_i32, c_i64, c_vp, c_i32, c_i64,
+                                      c_i64, c_i64, c_i64, c_i64, c_vp, c_sz, c_i32, c_vp, c_sz, c_vp]),
     "grws_spmm_fwd_static": (c_i32, [c_vp, c_vp, c_vp, c_i32, c_vp, c_i32, c_i64, c_vp, c_i32, c_i64,
                                      c_i64, c_i64, c_i64, c_i64, c_vp]),
     "grws_spmm_last_status": (c_i32, [c_vp, c_i32, c_vp]),

@@ -17,8 +17,10 @@ size_t spmm_warp_scratch_bytes(int64_t num_tiles_bound, int64_t N);
 bool spmm_tc5_supported(int dtype, int64_t N);
 int spmm_tc5_launch(const int64_t *, const int32_t *, const void *, int, const void *, int64_t,
                     void *, int, int64_t, int64_t, int64_t, int64_t, int64_t, void *, size_t,
-                    cudaStream_t);
+                    const void *, size_t, cudaStream_t);
 size_t spmm_tc5_scratch_bytes(int64_t num_tiles_bound, int64_t N);
+size_t spmm_tc5_plan_bytes(int64_t W, int64_t num_tiles_bound, int64_t K, int64_t N);
+int spmm_tc5_plan_build(const int64_t *, int64_t, int64_t, int64_t, int64_t, void *, size_t, cudaStream_t);
 int spmm_zero_output(void *C, int c_dtype, int64_t ldc, int64_t W, int64_t N, cudaStream_t stream);
 
 }  // namespace grws
@@ -48,11 +50,10 @@ int grws_spmm_resolve_algo(int dtype, int64_t N, int algo) {
     return algo;
 }
 
-__attribute__((visibility("default")))
-int grws_spmm_fwd(const int64_t *window_offset, const int32_t *cols, const void *vals,
-                  int val_dtype, const void *B, int b_dtype, int64_t ldb, void *C, int c_dtype,
-                  int64_t ldc, int64_t num_windows, int64_t num_tiles_bound, int64_t K, int64_t N,
-                  void *scratch, size_t scratch_bytes, int algo, void *stream) {
+static int spmm_fwd_any(const int64_t *window_offset, const int32_t *cols, const void *vals,
+                        int val_dtype, const void *B, int b_dtype, int64_t ldb, void *C, int c_dtype,
+                        int64_t ldc, int64_t num_windows, int64_t num_tiles_bound, int64_t K, int64_t N,
+                        void *scratch, size_t scratch_bytes, int algo, const void *plan, size_t plan_bytes, void *stream) {
     GRWS_REQUIRE(num_windows >= 0 && num_tiles_bound >= 0 && K >= 0 && N > 0, "negative size");
     if (num_windows == 0) return GRWS_OK;
     GRWS_REQUIRE(window_offset && C, "null pointer");
@@ -83,9 +84,48 @@ int grws_spmm_fwd(const int64_t *window_offset, const int32_t *cols, const void 
     }
     if (tc5)
         return spmm_tc5_launch(window_offset, cols, vals, val_dtype, B, ldb, C, c_dtype, ldc, num_windows,
-                               num_tiles_bound, K, N, scratch, scratch_bytes, st);
+                               num_tiles_bound, K, N, scratch, scratch_bytes, plan, plan_bytes, st);
     return spmm_warp_launch(window_offset, cols, vals, val_dtype, B, ldb, C, c_dtype, ldc, num_windows,
                             num_tiles_bound, K, N, scratch, scratch_bytes, st);
+}
+
+__attribute__((visibility("default")))
+int grws_spmm_fwd(const int64_t *window_offset, const int32_t *cols, const void *vals,
+                  int val_dtype, const void *B, int b_dtype, int64_t ldb, void *C, int c_dtype,
+                  int64_t ldc, int64_t num_windows, int64_t num_tiles_bound, int64_t K, int64_t N,
+                  void *scratch, size_t scratch_bytes, int algo, void *stream) {
+    return spmm_fwd_any(window_offset, cols, vals, val_dtype, B, b_dtype, ldb, C, c_dtype, ldc, num_windows,
+                        num_tiles_bound, K, N, scratch, scratch_bytes, algo, nullptr, 0, stream);
+}
+
+// The same product with the CTAs' tile ranges taken from a plan of this graph (grws_spmm_plan_build)
+// instead of searched at the start of the launch.  The plan only matters to the tcgen05 kernel; the
+// other paths ignore it, and so does that kernel when the plan was made for another shape.
+__attribute__((visibility("default")))
+int grws_spmm_fwd_planned(const int64_t *window_offset, const int32_t *cols, const void *vals,
+                          int val_dtype, const void *B, int b_dtype, int64_t ldb, void *C, int c_dtype,
+                          int64_t ldc, int64_t num_windows, int64_t num_tiles_bound, int64_t K, int64_t N,
+                          void *scratch, size_t scratch_bytes, int algo, const void *plan, size_t plan_bytes,
+                          void *stream) {
+    GRWS_REQUIRE(plan == nullptr || aligned16(plan), "the plan must be 16-byte aligned");
+    return spmm_fwd_any(window_offset, cols, vals, val_dtype, B, b_dtype, ldb, C, c_dtype, ldc, num_windows,
+                        num_tiles_bound, K, N, scratch, scratch_bytes, algo, plan, plan_bytes, stream);
+}
+
+__attribute__((visibility("default")))
+size_t grws_spmm_plan_bytes(int64_t num_windows, int64_t num_tiles_bound, int64_t K, int64_t N) {
+    if (num_windows < 0 || num_tiles_bound < 0 || K < 0 || N <= 0) return 0;
+    return spmm_tc5_plan_bytes(num_windows, num_tiles_bound, K, N);
+}
+
+__attribute__((visibility("default")))
+int grws_spmm_plan_build(const int64_t *window_offset, int64_t num_windows, int64_t num_tiles_bound, int64_t K,
+                         int64_t N, void *plan, size_t plan_bytes, void *stream) {
+    GRWS_REQUIRE(num_windows >= 0 && num_tiles_bound >= 0 && K >= 0 && N > 0, "negative size");
+    GRWS_REQUIRE(window_offset && plan, "null pointer");
+    GRWS_REQUIRE(aligned16(plan), "the plan must be 16-byte aligned");
+    return spmm_tc5_plan_build(window_offset, num_windows, num_tiles_bound, K, N, plan, plan_bytes,
+                               static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

@@ -86,6 +86,8 @@ constexpr int64_t SPLIT256_OPERAND_BYTES = 8ll << 20;   // dense operand size ab
 #ifndef GRWS_TC5_LW_TILES
 #define GRWS_TC5_LW_TILES 512
 #endif
+constexpr int PLAN_MAGIC = 0x504c4e31;                                    // first word of a valid plan
+constexpr int PLAN_LONG_WINDOW_STAGES = 16;                               // planned ranges: a window of more stages may be split
 constexpr int64_t LONG_WINDOW_TILES = GRWS_TC5_LW_TILES;                 // a cut inside a window of at most chunk >> 4 tiles moves to the window start
 constexpr long long WAIT_LIMIT_CYCLES = 3000000000ll;   // default: a wait gives up after about 1.5-2.5 s of SM clocks
 
@@ -105,6 +107,7 @@ struct Params {
     int *status;      // this call's status word (start of scratch)
     int *sticky;      // per-device word that keeps the worst status since it was last read (may be null)
     int *split_count; // [grid]: pieces of the split window that starts in CTA k which are finished (zeroed before the launch)
+    const int4 *plan; // tile ranges of the CTAs computed once per graph (spmm_plan_kernel), or null: every CTA searches its range
     int64_t W, N, ldb, ldc;
     int c_dtype;
     int is_bf16;
@@ -532,7 +535,27 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
         // ever split between CTAs
         const int64_t long_window = min(chunk >> 1, LONG_WINDOW_TILES);
         int64_t w_first, s, e;
-        warp_cut_pair(prm.window_offset, W, T, blockIdx.x, G, chunk, long_window, lane, &s, &e, &w_first);
+        // holders of the pieces of the windows this CTA's range starts / ends in (planned ranges only)
+        int plan_head_k0 = 0, plan_head_klast = 0, plan_tail_klast = 0;
+        bool planned = false;
+        if (prm.plan != nullptr) {
+            // ranges balanced by stage count, computed once per graph: header and the two cuts
+            // arrive in one round trip (the search below needs three dependent ones)
+            const int4 h0 = __ldg(prm.plan), h1 = __ldg(prm.plan + 1);
+            const int4 c0 = __ldg(prm.plan + 2 + 2 * blockIdx.x), c1 = __ldg(prm.plan + 3 + 2 * blockIdx.x);
+            const int4 n0 = __ldg(prm.plan + 4 + 2 * blockIdx.x);
+            const int64_t plan_w = ((int64_t)(uint32_t)h0.w << 32) | (uint32_t)h0.z;
+            const int64_t plan_t = ((int64_t)(uint32_t)h1.y << 32) | (uint32_t)h1.x;
+            // a plan made for another grid or another graph size is ignored
+            planned = h0.x == PLAN_MAGIC && h0.y == (int)G && plan_w == W && plan_t == T;
+            if (planned) {
+                s = ((int64_t)(uint32_t)c0.y << 32) | (uint32_t)c0.x;
+                w_first = ((int64_t)(uint32_t)c0.w << 32) | (uint32_t)c0.z;
+                e = ((int64_t)(uint32_t)n0.y << 32) | (uint32_t)n0.x;
+                plan_head_k0 = c1.x; plan_head_klast = c1.y; plan_tail_klast = c1.z;
+            }
+        }
+        if (!planned) warp_cut_pair(prm.window_offset, W, T, blockIdx.x, G, chunk, long_window, lane, &s, &e, &w_first);
         Walker wk;
         wk.init(prm.window_offset, W, s, e, blockIdx.x == 0 ? 0 : w_first, lane);
         if (warp == WALK_WARP && lane == 0) prof_stamp<PROF>(prm.dbg, 2);     // tile range found
@@ -674,10 +697,11 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
                     // the CTA that holds the window's first tile, and the one that arrives last sums the
                     // pieces in CTA order (the same order whoever is last) and writes the rows.  Cuts
                     // inside a split window are never moved, so its pieces are exactly the CTAs
-                    // a / chunk .. (b - 1) / chunk.  A holder that finds all the others already counted
+                    // a / chunk .. (b - 1) / chunk (planned ranges: the plan names the first and the last).  A holder that finds all the others already counted
                     // is the last one for sure and goes straight to the sum (its own piece was written by
                     // the very threads that read it back: no fence, no atomic).
-                    const int64_t k0 = wk.a / chunk, k_last = (wk.b - 1) / chunk;
+                    const int64_t k0 = planned ? (wk.head() ? plan_head_k0 : (int)blockIdx.x) : wk.a / chunk;
+                    const int64_t k_last = planned ? (wk.head() ? plan_head_klast : plan_tail_klast) : (wk.b - 1) / chunk;
                     if (threadIdx.x == EPILOGUE_WARP0 * 32) {
                         wait_for_zeroed_scratch();
                         int seen;
@@ -1069,6 +1093,131 @@ static int encode_b_map(CUtensorMap *map, const void *B, int is_bf16, int64_t K,
     if (r != CUDA_SUCCESS) return fail(GRWS_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
     return GRWS_OK;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Tile ranges computed once per graph.
+//
+// A CTA's run time follows its number of stages (a window of n tiles takes ceil(n / 8) stages; the
+// last one of a window is padded), not its number of tiles: equal tile counts leave the stage counts
+// of the CTAs 10-12 % apart on a power-law graph, and the slowest CTA sets the kernel's time.  The
+// plan cuts the prefix sum of the windows' stage counts into equal parts instead.  A cut that falls
+// into a window of at most PLAN_LONG_WINDOW_STAGES stages moves to the nearer end of that window; a
+// longer window is cut at a stage boundary and its pieces are put together as for searched ranges.
+// The search for the ranges (three dependent rounds of loads at the start of every launch) is
+// replaced by one load.
+//
+// Layout (int4 units): [0] magic, grid, W lo, W hi; [1] T lo, T hi, 0, 0; then per cut k = 0..grid:
+// [2 + 2k] first tile lo, hi, first window lo, hi; [3 + 2k] first / last holder of the window the range
+// starts in, last holder of the window it ends in, 0; behind them the stage prefix sums [W + 1].
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ int64_t plan_cut_tile(const int4 *plan, int k) {
+    const int4 c = plan[2 + 2 * k];
+    return ((int64_t)(uint32_t)c.y << 32) | (uint32_t)c.x;
+}
+
+__global__ void __launch_bounds__(1024) spmm_plan_kernel(const int64_t *__restrict__ off, int64_t W, int G, int4 *plan, int64_t *sp) {
+    __shared__ int64_t part[1024];
+    const int t = threadIdx.x;
+    const int64_t per = (W + 1023) / 1024;
+    const int64_t w0 = min(W, (int64_t)t * per), w1 = min(W, w0 + per);
+    int64_t sum = 0;
+    for (int64_t w = w0; w < w1; ++w) sum += (off[w + 1] - off[w] + STAGE_TILES - 1) / STAGE_TILES;
+    part[t] = sum;
+    __syncthreads();
+    for (int d = 1; d < 1024; d <<= 1) {
+        const int64_t v = t >= d ? part[t - d] : 0;
+        __syncthreads();
+        part[t] += v;
+        __syncthreads();
+    }
+    int64_t run = part[t] - sum;
+    for (int64_t w = w0; w < w1; ++w) {
+        sp[w] = run;
+        run += (off[w + 1] - off[w] + STAGE_TILES - 1) / STAGE_TILES;
+    }
+    const int64_t S = part[1023], T = off[W];
+    if (t == 1023) sp[W] = S;
+    __syncthreads();
+    // with fewer than 8 stages per CTA nothing is split: the pieces of a split window must all be
+    // non-empty, which equal stage shares guarantee only when there are at least as many stages as CTAs
+    const int64_t long_stages = S >= 8 * (int64_t)G ? PLAN_LONG_WINDOW_STAGES : INT64_MAX;
+    for (int k = t; k <= G; k += 1024) {
+        int64_t s, wf;
+        if (k == 0) { s = 0; wf = 0; }
+        else if (k == G || S == 0) { s = T; wf = W; }
+        else {
+            const int64_t tgt = ((int64_t)k * S) / G;          // S < 2^40 stages, k < 2^12
+            int64_t lo = 0, hi = W - 1;                        // last window whose prefix is <= tgt (it has stages)
+            while (lo < hi) {
+                const int64_t mid = (lo + hi + 1) >> 1;
+                if (sp[mid] <= tgt) lo = mid; else hi = mid - 1;
+            }
+            const int64_t a = off[lo], b = off[lo + 1], before = tgt - sp[lo], after = sp[lo + 1] - tgt;
+            if (before == 0) { s = a; wf = lo; }
+            else if (before + after <= long_stages) {
+                if (after < before) { s = b; wf = lo + 1; } else { s = a; wf = lo; }
+            } else { s = a + before * STAGE_TILES; wf = lo; }
+        }
+        plan[2 + 2 * k] = make_int4((int)(uint32_t)s, (int)(s >> 32), (int)(uint32_t)wf, (int)(wf >> 32));
+    }
+    __syncthreads();
+    for (int k = t; k <= G; k += 1024) {
+        int4 h = make_int4(k, k, k, 0);
+        if (k < G) {
+            const int4 c = plan[2 + 2 * k];
+            const int64_t s = plan_cut_tile(plan, k), e = plan_cut_tile(plan, k + 1);
+            const int64_t wf = ((int64_t)(uint32_t)c.w << 32) | (uint32_t)c.z;
+            if (s < e && wf < W && s > off[wf]) {
+                // the range starts inside window wf = [a, b): its pieces are held by the CTA whose range
+                // holds tile a up to the one whose range holds tile b - 1
+                const int64_t a = off[wf], b = off[wf + 1];
+                int j = k;
+                while (j > 0 && plan_cut_tile(plan, j) > a) --j;
+                h.x = j;
+                j = k;
+                while (j + 1 < G && plan_cut_tile(plan, j + 1) < b) ++j;
+                h.y = j;
+            }
+            if (s < e && e < T) {
+                const int4 n = plan[2 + 2 * (k + 1)];
+                const int64_t we = ((int64_t)(uint32_t)n.w << 32) | (uint32_t)n.z;
+                if (we < W && e > off[we] && off[we] >= s) {
+                    const int64_t b = off[we + 1];
+                    int j = k + 1;
+                    while (j + 1 < G && plan_cut_tile(plan, j + 1) < b) ++j;
+                    h.z = j;
+                }
+            }
+        }
+        plan[3 + 2 * k] = h;
+    }
+    if (t == 0) {
+        plan[0] = make_int4(PLAN_MAGIC, G, (int)(uint32_t)W, (int)(W >> 32));
+        plan[1] = make_int4((int)(uint32_t)T, (int)(T >> 32), 0, 0);
+    }
+}
+
+// number of persistent CTAs of one pass and the width of a pass, as the launch chooses them
+static void launch_shape(int sms, int64_t num_tiles_bound, int64_t K, int64_t N, int *G_out, int64_t *pass_n_out) {
+    // Width 256: one pass with two slabs per stage (one CTA per SM), or two passes of 128 columns.
+    // Two passes read the tiles twice but gather from half as many bytes of the dense operand,
+    // which then stays in L2 next to the tile stream, and they run two CTAs per SM: measured 4 %
+    // faster at 86 MB of operand, 20 % at 119 MB.  Small operands keep the single pass (half the
+    // launches).
+    const bool split = N == 256 && K * 512 > SPLIT256_OPERAND_BYTES;
+    const int64_t pass_n = (N == 128 || split) ? 128 : 256;
+    // one persistent CTA per SM slot, fewer for small products: a CTA range below ~64 tiles is mostly
+    // cuts through windows, whose pieces then cost more to put together than the tiles to multiply
+    int G = sms * (pass_n == 128 ? Cfg<1>::kCtasPerSm : Cfg<2>::kCtasPerSm);
+    const int64_t g_small = num_tiles_bound / MIN_TILES_PER_CTA;
+    if (g_small < G) G = g_small < 1 ? 1 : (int)g_small;
+    *G_out = G;
+    *pass_n_out = pass_n;
+}
+
+static size_t plan_bytes_for(int G, int64_t W) {
+    return sizeof(int4) * (2 + 2 * ((size_t)G + 1)) + sizeof(int64_t) * ((size_t)W + 1);
+}
 }  // namespace tc5
 
 bool spmm_tc5_supported(int dtype, int64_t N) {
@@ -1083,6 +1232,32 @@ size_t spmm_tc5_scratch_bytes(int64_t num_tiles_bound, int64_t N) {
     if (tc5::device_state(&d) != GRWS_OK) return 0;
     return tc5::STATUS_BYTES + tc5::DEBUG_BYTES + tc5::FIX_BYTES +
            (size_t)d->sms * tc5::SCRATCH_CTAS_PER_SM * 2 * TILE_ROWS * (size_t)N * sizeof(float);
+}
+
+// Bytes of the plan of one graph (0 when the device cannot be queried).
+size_t spmm_tc5_plan_bytes(int64_t W, int64_t num_tiles_bound, int64_t K, int64_t N) {
+    tc5::DeviceState *d = nullptr;
+    if (tc5::device_state(&d) != GRWS_OK) return 0;
+    int G = 0;
+    int64_t pass_n = 0;
+    tc5::launch_shape(d->sms, num_tiles_bound, K, N, &G, &pass_n);
+    return tc5::plan_bytes_for(G, W);
+}
+
+int spmm_tc5_plan_build(const int64_t *window_offset, int64_t W, int64_t num_tiles_bound, int64_t K, int64_t N,
+                        void *plan, size_t plan_bytes, cudaStream_t stream) {
+    using namespace tc5;
+    DeviceState *dev = nullptr;
+    if (int st = device_state(&dev)) return st;
+    int G = 0;
+    int64_t pass_n = 0;
+    launch_shape(dev->sms, num_tiles_bound, K, N, &G, &pass_n);
+    if (plan == nullptr || plan_bytes < plan_bytes_for(G, W))
+        return fail(GRWS_ERR_SCRATCH, "spmm plan too small: %zu < %zu bytes", plan_bytes, plan_bytes_for(G, W));
+    int4 *p = static_cast<int4 *>(plan);
+    spmm_plan_kernel<<<1, 1024, 0, stream>>>(window_offset, W, G, p, reinterpret_cast<int64_t *>(p + 2 + 2 * ((size_t)G + 1)));
+    GRWS_CUDA_TRY(cudaGetLastError());
+    return GRWS_OK;
 }
 
 __global__ void spmm_zero_rows_kernel(void *C, int64_t rows, int64_t row_bytes16, int64_t ld_bytes16) {
@@ -1107,7 +1282,7 @@ int spmm_zero_output(void *C, int c_dtype, int64_t ldc, int64_t W, int64_t N, cu
 int spmm_tc5_launch(const int64_t *window_offset, const int32_t *cols, const void *vals, int dtype,
                     const void *B, int64_t ldb, void *C, int c_dtype, int64_t ldc, int64_t W,
                     int64_t num_tiles_bound, int64_t K, int64_t N, void *scratch, size_t scratch_bytes,
-                    cudaStream_t stream) {
+                    const void *plan, size_t plan_bytes, cudaStream_t stream) {
     using namespace tc5;
     DeviceState *dev = nullptr;
     if (int st = device_state(&dev)) return st;
@@ -1134,18 +1309,15 @@ int spmm_tc5_launch(const int64_t *window_offset, const int32_t *cols, const voi
     prm.partial = reinterpret_cast<float *>(static_cast<char *>(scratch) + STATUS_BYTES + DEBUG_BYTES + FIX_BYTES);
     prm.W = W; prm.N = N; prm.ldb = ldb; prm.ldc = ldc; prm.c_dtype = c_dtype;
     prm.is_bf16 = dtype == GRWS_BF16 ? 1 : 0;
-    // Width 256: one pass with two slabs per stage (one CTA per SM), or two passes of 128 columns.
-    // Two passes read the tiles twice but gather from half as many bytes of the dense operand,
-    // which then stays in L2 next to the tile stream, and they run two CTAs per SM: measured 4 %
-    // faster at 86 MB of operand, 20 % at 119 MB.  Small operands keep the single pass (half the
-    // launches).
-    const bool split = N == 256 && K * 512 > SPLIT256_OPERAND_BYTES;
-    const int64_t pass_n = (N == 128 || split) ? 128 : 256;
-    // one persistent CTA per SM slot, fewer for small products: a CTA range below ~64 tiles is mostly
-    // cuts through windows, whose pieces then cost more to put together than the tiles to multiply
-    int G = dev->sms * (pass_n == 128 ? Cfg<1>::kCtasPerSm : Cfg<2>::kCtasPerSm);
-    const int64_t g_small = num_tiles_bound / MIN_TILES_PER_CTA;
-    if (g_small < G) G = g_small < 1 ? 1 : (int)g_small;
+    int G = 0;
+    int64_t pass_n = 0;
+    launch_shape(dev->sms, num_tiles_bound, K, N, &G, &pass_n);
+    prm.plan = nullptr;
+    if (plan != nullptr) {
+        if (plan_bytes < plan_bytes_for(G, W))
+            return fail(GRWS_ERR_SCRATCH, "spmm plan too small: %zu < %zu bytes", plan_bytes, plan_bytes_for(G, W));
+        prm.plan = static_cast<const int4 *>(plan);
+    }
     if ((size_t)G * sizeof(int) > FIX_BYTES) return fail(GRWS_ERR_UNSUPPORTED, "more CTAs (%d) than split-window counters", G);
     const size_t c_elem = c_dtype == GRWS_F32 ? 4 : 2;
     for (int64_t col0 = 0; col0 < N; col0 += pass_n) {
@@ -1284,5 +1456,5 @@ int grws_spmm_fwd_static(const int64_t *window_offset, const int32_t *cols, cons
     void *scratch = nullptr;
     if (int st = tc5::static_scratch_address(&scratch)) return st;
     return spmm_tc5_launch(window_offset, cols, vals, val_dtype, B, ldb, C, c_dtype, ldc, num_windows, num_tiles_bound,
-                           K, N, scratch, tc5::STATIC_SCRATCH_BYTES, static_cast<cudaStream_t>(stream));
+                           K, N, scratch, tc5::STATIC_SCRATCH_BYTES, nullptr, 0, static_cast<cudaStream_t>(stream));
 }

@@ -82,6 +82,25 @@ class BCSRGraph:
         self._shared[key] = (self._versions(), v)
         return v
 
+    def spmm_plan(self, K: int, N: int):
+        """Plan of the tcgen05 kernel's tile ranges for products of this graph with a [K, N] operand,
+        cached until the graph changes.  It is built at the second product of a shape, so a graph
+        that lives for one step (a sampled block) never pays for one: None then."""
+        if getattr(self, 'transient', False) or not self.window_offset.is_cuda:
+            return None
+        key = ("plan", int(K), int(N))
+        state = (self._versions(), self.window_offset._version)
+        hit = self._shared.get(key)
+        if hit is None or hit[0] != state:
+            self._shared[key] = (state, None)
+            return None
+        if hit[1] is None:
+            from ..core import spmm_plan
+            plan = spmm_plan(self.window_offset, self.original_col_indices.numel() // self.tile_cols, K, N)
+            self._shared[key] = (state, plan)
+            return plan
+        return hit[1]
+
     def transposed(self, num_cols: Optional[int] = None, dtype: Optional[torch.dtype] = None) -> 'BCSRGraph':
         """BCSR of A^T with ``num_cols`` rows (default ``self.num_cols``), built on the device once
         and cached; the backward product ``A^T @ G`` runs the forward kernel on it."""
@@ -101,6 +120,7 @@ class BCSRGraph:
                        window_offset=wo, original_col_indices=cols, values_condensed=vals,
                        device=vals.device, num_rows=n, num_cols=self.num_windows * self.tile_rows,
                        values_dtype=dtype)
+        gt.transient = getattr(self, 'transient', False)
         self._shared[key] = (self._versions(), gt)
         return gt
 

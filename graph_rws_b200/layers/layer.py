@@ -29,7 +29,9 @@ def _spmm_graph(graph, dense):
     pad = (-n) % 8
     if pad:
         dense = F.pad(dense, (0, pad))
-    out = core.spmm_raw(graph.window_offset, graph.original_col_indices, vals, dense)
+    planner = getattr(graph, 'spmm_plan', None)
+    plan = planner(dense.shape[0], dense.shape[1]) if planner is not None else None
+    out = core.spmm_raw(graph.window_offset, graph.original_col_indices, vals, dense, plan=plan)
     return out[:, :n] if pad else out
 
 

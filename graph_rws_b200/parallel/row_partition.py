@@ -173,7 +173,8 @@ class DistributedSpMM:
         from .. import core
         h_full = all_gather_rows(h_local, self.part, self.group)
         g = self.local
-        out = core.spmm_raw(g.window_offset, g.original_col_indices, g.values_as(h_full.dtype), h_full.contiguous())
+        out = core.spmm_raw(g.window_offset, g.original_col_indices, g.values_as(h_full.dtype), h_full.contiguous(),
+                            plan=g.spmm_plan(h_full.shape[0], h_full.shape[1]))
         lo, hi = self.part.rows(self.rank)
         return out[:hi - lo]
 
@@ -218,6 +219,9 @@ class RowShardedGraph:
 
     def values_as(self, dtype):
         return self.local.values_as(dtype)
+
+    def spmm_plan(self, K, N):
+        return self.local.spmm_plan(K, N)
 
     def gather_dense(self, dense_local):
         # a product returns whole windows: rows past the rank's last row are padding

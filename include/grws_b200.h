@@ -81,6 +81,32 @@ int grws_spmm_fwd(const int64_t *window_offset, const int32_t *cols, const void 
                   void *scratch, size_t scratch_bytes, int algo, void *stream);
 
 /* ------------------------------------------------------------------------------------------
+ * SpMM on a graph that is multiplied many times (full-graph training: the same BCSR every epoch).
+ * The reference has no counterpart (its kernel maps one thread block to one window,
+ * core/include/spmm_tc.cuh:48-50).  The tcgen05 kernel gives each persistent CTA a contiguous range
+ * of tiles; grws_spmm_fwd finds the ranges at the start of every launch by a search over
+ * `window_offset`, with equal tile counts.  A plan holds ranges computed once for a graph, with
+ * equal numbers of pipeline stages (what a CTA's run time follows), so the slowest CTA finishes
+ * earlier and the search is gone:
+ *   grws_spmm_plan_bytes : size of the plan buffer for this shape on the current device;
+ *   grws_spmm_plan_build : queues one small kernel that fills `plan` from `window_offset`; call it
+ *                          again whenever `window_offset` changes;
+ *   grws_spmm_fwd_planned: grws_spmm_fwd with the plan (null = none).  The plan is used by the
+ *                          tcgen05 kernel only, and only if it was built for the same num_windows,
+ *                          tile count, K class and N on a device of the same size; otherwise the
+ *                          launch searches its ranges as grws_spmm_fwd does.  A plan built from
+ *                          another graph of the same shape gives wrong results.
+ * ------------------------------------------------------------------------------------------ */
+size_t grws_spmm_plan_bytes(int64_t num_windows, int64_t num_tiles_bound, int64_t K, int64_t N);
+int grws_spmm_plan_build(const int64_t *window_offset, int64_t num_windows, int64_t num_tiles_bound,
+                         int64_t K, int64_t N, void *plan, size_t plan_bytes, void *stream);
+int grws_spmm_fwd_planned(const int64_t *window_offset, const int32_t *cols, const void *vals,
+                          int val_dtype, const void *B, int b_dtype, int64_t ldb, void *C, int c_dtype,
+                          int64_t ldc, int64_t num_windows, int64_t num_tiles_bound, int64_t K, int64_t N,
+                          void *scratch, size_t scratch_bytes, int algo, const void *plan,
+                          size_t plan_bytes, void *stream);
+
+/* ------------------------------------------------------------------------------------------
  * Status of the tcgen05 SpMM launches.  The reference has no counterpart: its kernels cannot
  * report anything (errors are host-side TORCH_CHECKs, core/wrapper/spmm_wrapper.cu:48-51).
  * Every wait of the tcgen05 kernel on a shared-memory barrier is bounded; a launch whose wait
