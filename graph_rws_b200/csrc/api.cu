@@ -15,6 +15,7 @@ int spmm_warp_launch(const int64_t *, const int32_t *, const void *, int, const 
 size_t spmm_warp_scratch_bytes(int64_t num_tiles_bound, int64_t N);
 // spmm_tcgen05.cu
 bool spmm_tc5_supported(int dtype, int64_t N);
+bool spmm_tc5_preferred(int dtype, int64_t N, int64_t num_tiles_bound);
 int spmm_tc5_launch(const int64_t *, const int32_t *, const void *, int, const void *, int64_t,
                     void *, int, int64_t, int64_t, int64_t, int64_t, int64_t, void *, size_t,
                     const void *, size_t, cudaStream_t);
@@ -46,7 +47,8 @@ size_t grws_spmm_scratch_bytes(int64_t num_windows, int64_t num_tiles_bound, int
 
 __attribute__((visibility("default")))
 int grws_spmm_resolve_algo(int dtype, int64_t N, int algo) {
-    if (algo == GRWS_SPMM_AUTO) return spmm_tc5_supported(dtype, N) ? GRWS_SPMM_TCGEN05 : GRWS_SPMM_WARP_MMA;
+    // (for a width below 128 the answer assumes a large product: small ones stay on the warp-MMA kernel)
+    if (algo == GRWS_SPMM_AUTO) return spmm_tc5_preferred(dtype, N, INT64_MAX) ? GRWS_SPMM_TCGEN05 : GRWS_SPMM_WARP_MMA;
     return algo;
 }
 
@@ -75,10 +77,10 @@ static int spmm_fwd_any(const int64_t *window_offset, const int32_t *cols, const
     bool tc5 = false;
     if (algo == GRWS_SPMM_TCGEN05) {
         if (!spmm_tc5_supported(val_dtype, N))
-            return fail(GRWS_ERR_UNSUPPORTED, "tcgen05 path needs fp16/bf16 and N a multiple of 64 (N=%lld)", (long long)N);
+            return fail(GRWS_ERR_UNSUPPORTED, "tcgen05 path needs fp16/bf16 and N = 256 or a multiple of 8 up to 128 (N=%lld)", (long long)N);
         tc5 = true;
     } else if (algo == GRWS_SPMM_AUTO) {
-        tc5 = spmm_tc5_supported(val_dtype, N);
+        tc5 = spmm_tc5_preferred(val_dtype, N, num_tiles_bound);
     } else if (algo != GRWS_SPMM_WARP_MMA) {
         return fail(GRWS_ERR_INVALID, "unknown algo %d", algo);
     }

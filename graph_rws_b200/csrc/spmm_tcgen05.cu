@@ -86,6 +86,12 @@ constexpr int64_t SPLIT256_OPERAND_BYTES = 8ll << 20;   // dense operand size ab
 #ifndef GRWS_TC5_LW_TILES
 #define GRWS_TC5_LW_TILES 512
 #endif
+#ifndef GRWS_TC5_AUTO_MIN_N
+#define GRWS_TC5_AUTO_MIN_N 16
+#endif
+#ifndef GRWS_TC5_AUTO_MIN_TILES
+#define GRWS_TC5_AUTO_MIN_TILES 32768
+#endif
 constexpr int PLAN_MAGIC = 0x504c4e31;                                    // first word of a valid plan
 constexpr int PLAN_LONG_WINDOW_STAGES = 16;                               // planned ranges: a window of more stages may be split
 constexpr int64_t LONG_WINDOW_TILES = GRWS_TC5_LW_TILES;                 // a cut inside a window of at most chunk >> 4 tiles moves to the window start
@@ -108,7 +114,8 @@ struct Params {
     int *sticky;      // per-device word that keeps the worst status since it was last read (may be null)
     int *split_count; // [grid]: pieces of the split window that starts in CTA k which are finished (zeroed before the launch)
     const int4 *plan; // tile ranges of the CTAs computed once per graph (spmm_plan_kernel), or null: every CTA searches its range
-    int64_t W, N, ldb, ldc;
+    int64_t W, N, ldb, ldc;   // N: width of the pass as the kernel lays it out (128 or 256)
+    int n_valid;      // features of the pass that exist in B and C (a multiple of 8, <= N); the rest is computed on zeros and dropped
     int c_dtype;
     int is_bf16;
     int skip;         // profiling build only
@@ -429,7 +436,7 @@ __device__ __forceinline__ void raise(Params const &prm, SharedStorage *ss, int 
 // 32 offsets per coalesced load); warp quarter q writes features 32q .. 32q+31 of every slab.
 template <int NH>
 __device__ __noinline__ void zero_fill_empty_windows(const int64_t *__restrict__ window_offset, void *C, int64_t ldc, int c_dtype,
-                                                    int64_t W, int q, int lane) {
+                                                    int64_t W, int n_valid, int q, int lane) {
     const int64_t per = (W + gridDim.x - 1) / gridDim.x;
     const int64_t w_lo = (int64_t)blockIdx.x * per, w_hi = min(W, w_lo + per);
     for (int64_t wb = w_lo; wb < w_hi; wb += 32) {
@@ -441,6 +448,7 @@ __device__ __noinline__ void zero_fill_empty_windows(const int64_t *__restrict__
             m &= m - 1;
 #pragma unroll
             for (int h = 0; h < NH; ++h) {
+                if (h * SLAB + 32 * q + lane >= n_valid) continue;
                 const int64_t o0 = (w0 * TILE_ROWS) * ldc + h * SLAB + 32 * q + lane;
                 for (int r = 0; r < 16; ++r) {
                     const int64_t o = o0 + r * ldc;
@@ -455,13 +463,14 @@ __device__ __noinline__ void zero_fill_empty_windows(const int64_t *__restrict__
 // Sum of the pieces of split window w (held by CTAs k0 .. k_last, the first one in its tail slot,
 // the others in their head slots), in CTA order, written to the window's rows.
 template <int NH>
-__device__ __noinline__ void sum_pieces(const float *partial, int64_t N, void *C, int64_t ldc, int c_dtype, int64_t w, int64_t k0,
+__device__ __noinline__ void sum_pieces(const float *partial, int64_t N, int n_valid, void *C, int64_t ldc, int c_dtype, int64_t w, int64_t k0,
                                        int64_t k_last, int q, int lane) {
     __threadfence();
     const int64_t elems = TILE_ROWS * N;
 #pragma unroll
     for (int h = 0; h < NH; ++h) {
         const int64_t f = h * SLAB + 32 * q + lane;
+        if (f >= n_valid) continue;
         float acc[16];
         const float *p0 = partial + (2 * k0 + 1) * elems + f;
 #pragma unroll
@@ -621,7 +630,7 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
             // Windows without tiles produce zero rows.  They are dealt to all CTAs here, while the
             // pipeline fills, instead of being written by whichever CTA's tile range they border:
             // a run of empty windows (padded blocks, isolated nodes) would serialise on that one CTA.
-            if (!(skip & SKIP_STORE)) zero_fill_empty_windows<NH>(prm.window_offset, prm.C, prm.ldc, prm.c_dtype, W, q, lane);
+            if (!(skip & SKIP_STORE)) zero_fill_empty_windows<NH>(prm.window_offset, prm.C, prm.ldc, prm.c_dtype, W, prm.n_valid, q, lane);
             for (;;) {
                 const bool more = wk.next_segment(lane);
                 if (!more) break;                          // the same in all four warps: they walk the same ranges
@@ -669,17 +678,28 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
                     {
                         constexpr int CPR = SLAB * NH * 2 / 16;            // 16-byte pieces per row
                         char *dst = static_cast<char *>(prm.C) + (w * TILE_ROWS) * prm.ldc * 2;
+                        if (prm.n_valid == SLAB * NH) {
 #pragma unroll
-                        for (int c = threadIdx.x; c < TILE_ROWS * CPR; c += NUM_EPILOGUE) {
-                            const int r = c / CPR, k = c % CPR;
-                            const uint4 val = *reinterpret_cast<const uint4 *>(staging + r * (SLAB * NH * 2) + k * 16);
-                            asm volatile("st.global.L2::cache_hint.v4.b32 [%0], {%1, %2, %3, %4}, %5;"
-                                         ::"l"(dst + (int64_t)r * prm.ldc * 2 + k * 16), "r"(val.x), "r"(val.y), "r"(val.z), "r"(val.w), "l"(pol) : "memory");
+                            for (int c = threadIdx.x; c < TILE_ROWS * CPR; c += NUM_EPILOGUE) {
+                                const int r = c / CPR, k = c % CPR;
+                                const uint4 val = *reinterpret_cast<const uint4 *>(staging + r * (SLAB * NH * 2) + k * 16);
+                                asm volatile("st.global.L2::cache_hint.v4.b32 [%0], {%1, %2, %3, %4}, %5;"
+                                             ::"l"(dst + (int64_t)r * prm.ldc * 2 + k * 16), "r"(val.x), "r"(val.y), "r"(val.z), "r"(val.w), "l"(pol) : "memory");
+                            }
+                        } else {
+                            const int cpr = prm.n_valid / 8;               // a narrow operand: the row's first n_valid features
+                            for (int c = threadIdx.x; c < TILE_ROWS * cpr; c += NUM_EPILOGUE) {
+                                const int r = c / cpr, k = c % cpr;
+                                const uint4 val = *reinterpret_cast<const uint4 *>(staging + r * (SLAB * NH * 2) + k * 16);
+                                asm volatile("st.global.L2::cache_hint.v4.b32 [%0], {%1, %2, %3, %4}, %5;"
+                                             ::"l"(dst + (int64_t)r * prm.ldc * 2 + k * 16), "r"(val.x), "r"(val.y), "r"(val.z), "r"(val.w), "l"(pol) : "memory");
+                            }
                         }
                     }
                 } else if (!partial) {
 #pragma unroll
                     for (int h = 0; h < NH; ++h) {
+                        if (h * SLAB + 32 * q + lane >= prm.n_valid) continue;
                         const int64_t base = (w * TILE_ROWS) * prm.ldc + h * SLAB + 32 * q + lane;
 #pragma unroll
                         for (int r = 0; r < 16; ++r)
@@ -718,7 +738,7 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
                         }
                         epilogue_sync();
                     }
-                    if (*reinterpret_cast<volatile int *>(&ss->last_piece)) sum_pieces<NH>(prm.partial, prm.N, prm.C, prm.ldc, prm.c_dtype, w, k0, k_last, q, lane);
+                    if (*reinterpret_cast<volatile int *>(&ss->last_piece)) sum_pieces<NH>(prm.partial, prm.N, prm.n_valid, prm.C, prm.ldc, prm.c_dtype, w, k0, k_last, q, lane);
                 }
             }
             if (threadIdx.x == EPILOGUE_WARP0 * 32) prof_stamp<PROF>(prm.dbg, 5);      // last rows written
@@ -736,6 +756,9 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
         // cannot be moved across them and costs the chain ~45 cycles per copy instead of ~20 -- and
         // the first batch is loaded while the ring slot is still being waited for.
         const uint32_t gs = (uint32_t)(warp - PRODUCER_WARP0);
+        // An operand of at most 64 features (one slab, NH = 1): only the first 64-feature half of a row
+        // is fetched; the MMAs still multiply the whole slot, the other half's results are never read.
+        const bool narrow = NH == 1 && prm.n_valid <= 64;
         if (elect_one()) {
             constexpr uint32_t D = (uint32_t)C::kMetaDepth;
             const uint64_t keep = policy_keep(), stream_pol = policy_stream();
@@ -824,7 +847,7 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
                     mbar_arrive(full_bar);
                 } else {
                     // bytes the K-steps of this stage bring in: 16 slots x 128 features x NH slabs each
-                    mbar_expect_tx(full_bar, (uint32_t)(nmma * 16 * SLAB * 2 * NH));
+                    mbar_expect_tx(full_bar, (uint32_t)(nmma * 16 * SLAB * 2 * NH) >> (narrow ? 1 : 0));
                     armed = true;
                     armed_ph = gph;
                     // copy (K-step m, slot group g, feature half oh): slots 4g .. 4g+3 of K-step m land in
@@ -844,6 +867,7 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
                                     const int4 rr = r[mm * 4 + g];
 #pragma unroll
                                     for (int oh = 0; oh < 2; ++oh) {
+                                        if (oh == 1 && narrow) break;      // features 64 .. 127 do not exist: nothing to fetch
                                         const uint32_t off = (uint32_t)((m0 + mm) * NH * A_MMA_BYTES + (g >> 1) * A_SBO + oh * A_LBO + ((4 * g) & 7) * 128);
 #pragma unroll
                                         for (int h = 0; h < NH; ++h)
@@ -1205,7 +1229,7 @@ static void launch_shape(int sms, int64_t num_tiles_bound, int64_t K, int64_t N,
     // faster at 86 MB of operand, 20 % at 119 MB.  Small operands keep the single pass (half the
     // launches).
     const bool split = N == 256 && K * 512 > SPLIT256_OPERAND_BYTES;
-    const int64_t pass_n = (N == 128 || split) ? 128 : 256;
+    const int64_t pass_n = (N <= 128 || split) ? 128 : 256;     // widths below 128 run as one pass over a zero-extended operand
     // one persistent CTA per SM slot, fewer for small products: a CTA range below ~64 tiles is mostly
     // cuts through windows, whose pieces then cost more to put together than the tiles to multiply
     int G = sms * (pass_n == 128 ? Cfg<1>::kCtasPerSm : Cfg<2>::kCtasPerSm);
@@ -1220,8 +1244,19 @@ static size_t plan_bytes_for(int G, int64_t W) {
 }
 }  // namespace tc5
 
+// fp16 / bf16 operands of width 256, or of any multiple of 8 up to 128 (narrower operands are
+// multiplied as 128 features of which the missing ones are zeros)
 bool spmm_tc5_supported(int dtype, int64_t N) {
-    return (dtype == GRWS_F16 || dtype == GRWS_BF16) && (N == 128 || N == 256);
+    return (dtype == GRWS_F16 || dtype == GRWS_BF16) && (N == 256 || (N >= 8 && N <= 128 && N % 8 == 0));
+}
+
+// What GRWS_SPMM_AUTO picks the tcgen05 kernel for: widths 128 and 256 always; narrower operands when
+// the product is large (the kernel costs the same for every width up to 64 and up to 128, so it wins
+// by 25-35 % from 16 features on -- measured on a 114 M-entry graph and on a power-law graph of 2.5 M
+// entries -- but its fixed cost of ~20 us is above the warp-MMA kernel's on a small graph).
+bool spmm_tc5_preferred(int dtype, int64_t N, int64_t num_tiles_bound) {
+    if (!spmm_tc5_supported(dtype, N)) return false;
+    return N >= 128 || (N >= GRWS_TC5_AUTO_MIN_N && num_tiles_bound >= GRWS_TC5_AUTO_MIN_TILES);
 }
 
 // Scratch of one call: status word | split-window counters | profiling counters | two fp32 partial
@@ -1230,6 +1265,7 @@ size_t spmm_tc5_scratch_bytes(int64_t num_tiles_bound, int64_t N) {
     (void)num_tiles_bound;
     tc5::DeviceState *d = nullptr;
     if (tc5::device_state(&d) != GRWS_OK) return 0;
+    if (N < 128) N = 128;                     // partial tiles are laid out at the width of a pass
     return tc5::STATUS_BYTES + tc5::DEBUG_BYTES + tc5::FIX_BYTES +
            (size_t)d->sms * tc5::SCRATCH_CTAS_PER_SM * 2 * TILE_ROWS * (size_t)N * sizeof(float);
 }
@@ -1324,8 +1360,10 @@ int spmm_tc5_launch(const int64_t *window_offset, const int32_t *cols, const voi
         prm.B = static_cast<const char *>(B) + col0 * 2;
         prm.C = static_cast<char *>(C) + col0 * c_elem;
         prm.N = pass_n;
+        prm.n_valid = (int)(N - col0 < pass_n ? N - col0 : pass_n);
+        // the tensor map covers the features that exist: the TMA unit fills the rest of a 64-feature box with zeros
         alignas(64) CUtensorMap b_map;
-        if (int st = encode_b_map(&b_map, prm.B, prm.is_bf16, K, pass_n, ldb)) return st;
+        if (int st = encode_b_map(&b_map, prm.B, prm.is_bf16, K, prm.n_valid, ldb)) return st;
         // the status word is cleared once per call, the split-window counters before every pass
         if (col0 == 0) zero_words_kernel<<<1, 256, 0, stream>>>(static_cast<int *>(scratch), (int)(STATUS_BYTES / sizeof(int)) + G);
         else zero_words_kernel<<<1, 256, 0, stream>>>(prm.split_count, G);

@@ -78,6 +78,44 @@ def test_tcgen05_power_law_graph(oracle, dt, N, out):
     check_spmm_tolerance(C, C_ref, None, f"tcgen05 power-law N={N} {dt}")
 
 
+@pytest.mark.parametrize("dt,N,out", [("f16", 48, "f16"), ("bf16", 64, "f32"), ("f16", 96, "f16"), ("f16", 8, "f32"), ("bf16", 120, "bf16")])
+def test_tcgen05_narrow_operands(oracle, dt, N, out):
+    """Widths below 128: the operand is multiplied as 128 features of which the missing ones are
+    zeros (the TMA unit fills them in), and only the existing features are written.  Output rows are
+    placed in a wider buffer whose other columns must stay untouched."""
+    from graph_rws_b200 import core
+    from graph_rws_b200.core import _native
+    from graph_rws_b200.data import synthetic
+    dev = torch.device("cuda")
+    g = synthetic.sym_normalized_csr(20000, *synthetic.chung_lu_edges(20000, 300000, 2.1, 23))
+    wo, cols, vals = oracle.csr_to_bcsr(g.num_nodes, g.row_ptr, g.col_idx, g.values)
+    C, C_ref = _run(oracle, wo, cols, vals, g.num_nodes, N, dt, core.ALGO_TCGEN05, seed=7, out_dtype=DT[out])
+    if out == "bf16":
+        C_ref = torch.from_numpy(C_ref).bfloat16().float().numpy()
+        assert np.abs(C - C_ref).max() <= 2 ** -7 * np.abs(C_ref).max() + 1e-6
+    else:
+        check_spmm_tolerance(C, C_ref, None, f"tcgen05 narrow N={N} {dt}")
+    # strided output: columns N .. ldc-1 of the buffer belong to somebody else
+    lib = _native.lib()
+    dtype = DT[dt]
+    W, T, ldc = len(wo) - 1, int(wo[-1]), 136
+    B = torch.randn(g.num_nodes, N, generator=torch.Generator().manual_seed(7)).to(dtype).to(dev)
+    vals_d = torch.from_numpy(vals).to(dtype).to(dev)
+    wo_d, cols_d = torch.from_numpy(wo).to(dev), torch.from_numpy(cols).to(dev)
+    buf = torch.full((W * 16, ldc), 7.0, dtype=dtype, device=dev)
+    nbytes = lib.grws_spmm_scratch_bytes(W, T, N, core.ALGO_TCGEN05)
+    scratch = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    code = {"f16": 1, "bf16": 2}[dt]
+    _native.check(lib.grws_spmm_fwd(wo_d.data_ptr(), cols_d.data_ptr(), vals_d.data_ptr(), code, B.data_ptr(), code, N,
+                                    buf.data_ptr(), code, ldc, W, T, g.num_nodes, N, scratch.data_ptr(), nbytes,
+                                    core.ALGO_TCGEN05, torch.cuda.current_stream().cuda_stream))
+    core.check_device_status()
+    assert bool((buf[:, N:] == 7.0).all()), "columns beyond N were written"
+    ref16 = oracle.spmm_fwd(wo, cols, vals_d.float().cpu().numpy(), B.float().cpu().numpy())
+    if dt == "f16":
+        check_spmm_tolerance(buf[:, :N].float().cpu().numpy(), ref16, None, f"strided narrow N={N}")
+
+
 def test_tcgen05_and_warp_paths_agree(oracle):
     from graph_rws_b200 import core
     c = load_case(os.path.join(GOLDEN, "bcsr_chunglu_600.npz"))
