@@ -78,16 +78,25 @@ def spmm_plan(window_offset, num_tiles, K, N):
     return plan
 
 
-def spmm_raw(window_offset, cols, vals, B, out_dtype=None, algo=None, num_tiles_bound=None, check=False, plan=None):
+def spmm_raw(window_offset, cols, vals, B, out_dtype=None, algo=None, num_tiles_bound=None, check=False, plan=None,
+             out=None):
     """C[W*16, N] = A_bcsr @ B with values already in B's dtype and N % 8 == 0.
 
     ``check=True`` synchronises and raises if a tcgen05 launch reported a timed-out wait;
-    ``plan`` is the result of ``spmm_plan`` for this graph, K and N (optional)."""
+    ``plan`` is the result of ``spmm_plan`` for this graph, K and N (optional); ``out`` is a
+    [W*16, N] tensor to write into, possibly a column slice of a wider matrix (rows 16-byte
+    aligned, unit column stride)."""
     lib = _native.lib()
     W = window_offset.shape[0] - 1
     K, N = B.shape
-    out_dtype = out_dtype or B.dtype
-    C = torch.empty((W * 16, N), dtype=out_dtype, device=B.device)
+    if out is None:
+        out_dtype = out_dtype or B.dtype
+        C = torch.empty((W * 16, N), dtype=out_dtype, device=B.device)
+    else:
+        C, out_dtype = out, out.dtype
+        if (tuple(C.shape) != (W * 16, N) or C.stride(1) != 1 or C.device != B.device
+                or (C.stride(0) * C.element_size()) % 16 or C.data_ptr() % 16):
+            raise RuntimeError("out must be a [W*16, N] matrix on B's device with 16-byte aligned rows")
     if W == 0:
         return C
     T = cols.numel() // 8 if num_tiles_bound is None else int(num_tiles_bound)
@@ -97,12 +106,12 @@ def spmm_raw(window_offset, cols, vals, B, out_dtype=None, algo=None, num_tiles_
     if plan is not None:
         _native.check(lib.grws_spmm_fwd_planned(
             _ptr(window_offset), _ptr(cols), _ptr(vals), _DT[vals.dtype], _ptr(B), _DT[B.dtype], B.stride(0),
-            C.data_ptr(), _DT[out_dtype], N, W, T, K, N, scratch.data_ptr(), scratch.numel(), algo,
+            C.data_ptr(), _DT[out_dtype], C.stride(0), W, T, K, N, scratch.data_ptr(), scratch.numel(), algo,
             plan.data_ptr(), plan.numel(), _stream(B.device)))
     else:
         _native.check(lib.grws_spmm_fwd(
             _ptr(window_offset), _ptr(cols), _ptr(vals), _DT[vals.dtype], _ptr(B), _DT[B.dtype], B.stride(0),
-            C.data_ptr(), _DT[out_dtype], N, W, T, K, N, scratch.data_ptr(), scratch.numel(), algo,
+            C.data_ptr(), _DT[out_dtype], C.stride(0), W, T, K, N, scratch.data_ptr(), scratch.numel(), algo,
             _stream(B.device)))
     if check:
         check_device_status(B.device)

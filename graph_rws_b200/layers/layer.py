@@ -20,6 +20,11 @@ def _spmm_graph(graph, dense):
 
     A graph may bring its own product through a ``gather_dense`` hook: a row-sharded graph
     (parallel.RowShardedGraph) all-gathers the row shards of ``dense`` before its local product."""
+    pipelined = getattr(graph, 'gathered_product', None)
+    if pipelined is not None:
+        out = pipelined(dense)
+        if out is not None:
+            return out
     gather = getattr(graph, 'gather_dense', None)
     if gather is not None:
         dense = gather(dense)
@@ -110,7 +115,14 @@ class BCSRGraphConv(nn.Module):
         aggregate_first = (not features.requires_grad and features.shape[1] <= self.out_feats
                            and not hasattr(graph, 'gather_dense') and not core._timing_enabled)
         fn = BCSRAggregateFirstFunction if aggregate_first else BCSRSPMMFunction
-        h_neigh = fn.apply(graph, features, self.weight_neigh, self.warps_per_block)
+        # An output width that is no multiple of 8 (41 or 47 classes) is computed at the next multiple
+        # with zero weight columns and cut at the end: the SpMM needs 16-byte rows anyway, and the
+        # GEMMs around it (X W, dY W^T, X^T dY) otherwise fall to unaligned library kernels several
+        # times slower (0.46 ms instead of 0.07 ms each on 233 k rows x 256 -> 41).
+        pad = (-self.out_feats) % 8
+        w_neigh = F.pad(self.weight_neigh, (0, pad)) if pad else self.weight_neigh
+        w_self = F.pad(self.weight_self, (0, pad)) if pad else self.weight_self
+        h_neigh = fn.apply(graph, features, w_neigh, self.warps_per_block)
         target_rows = h_neigh.shape[0]
         if features_target is not None:
             h_in_self = features_target
@@ -118,10 +130,11 @@ class BCSRGraphConv(nn.Module):
             h_in_self = features[:target_rows]          # target nodes first
         else:
             h_in_self = F.pad(features, (0, 0, 0, target_rows - features.shape[0]))
-        h_self = torch.matmul(h_in_self, self.weight_self)
+        h_self = torch.matmul(h_in_self, w_self)
         # the SpMM returns whole windows (W*16 rows); trim or pad to the self path
         if h_neigh.shape[0] > h_self.shape[0]:
             h_neigh = h_neigh[:h_self.shape[0]]
         elif h_neigh.shape[0] < h_self.shape[0]:
             h_neigh = F.pad(h_neigh, (0, 0, 0, h_self.shape[0] - h_neigh.shape[0]))
-        return h_neigh + h_self
+        out = h_neigh + h_self
+        return out[:, :self.out_feats] if pad else out
