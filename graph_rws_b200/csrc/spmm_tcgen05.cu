@@ -491,10 +491,14 @@ __device__ __noinline__ void sum_pieces(const float *partial, int64_t N, int n_v
     }
 }
 
-template <int NH, bool PROF>
+// NARROW: the operand has fewer features than the pass is wide (prm.n_valid < 128, one slab); the
+// full-width kernel carries none of the tests that needs.
+template <int NH, bool PROF, bool NARROW = false>
 __global__ void __launch_bounds__(NUM_THREADS, Cfg<NH>::kCtasPerSm)
 spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
     using C = Cfg<NH>;
+    static_assert(!NARROW || NH == 1, "narrow operands run as one slab");
+    const int n_valid = NARROW ? prm.n_valid : SLAB * NH;
     extern __shared__ uint8_t smem_raw[];
     // the swizzled operand atoms must start on 1024-byte boundaries
     uint8_t *ring_g = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -630,7 +634,7 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
             // Windows without tiles produce zero rows.  They are dealt to all CTAs here, while the
             // pipeline fills, instead of being written by whichever CTA's tile range they border:
             // a run of empty windows (padded blocks, isolated nodes) would serialise on that one CTA.
-            if (!(skip & SKIP_STORE)) zero_fill_empty_windows<NH>(prm.window_offset, prm.C, prm.ldc, prm.c_dtype, W, prm.n_valid, q, lane);
+            if (!(skip & SKIP_STORE)) zero_fill_empty_windows<NH>(prm.window_offset, prm.C, prm.ldc, prm.c_dtype, W, n_valid, q, lane);
             for (;;) {
                 const bool more = wk.next_segment(lane);
                 if (!more) break;                          // the same in all four warps: they walk the same ranges
@@ -678,7 +682,7 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
                     {
                         constexpr int CPR = SLAB * NH * 2 / 16;            // 16-byte pieces per row
                         char *dst = static_cast<char *>(prm.C) + (w * TILE_ROWS) * prm.ldc * 2;
-                        if (prm.n_valid == SLAB * NH) {
+                        if (!NARROW) {
 #pragma unroll
                             for (int c = threadIdx.x; c < TILE_ROWS * CPR; c += NUM_EPILOGUE) {
                                 const int r = c / CPR, k = c % CPR;
@@ -687,7 +691,7 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
                                              ::"l"(dst + (int64_t)r * prm.ldc * 2 + k * 16), "r"(val.x), "r"(val.y), "r"(val.z), "r"(val.w), "l"(pol) : "memory");
                             }
                         } else {
-                            const int cpr = prm.n_valid / 8;               // a narrow operand: the row's first n_valid features
+                            const int cpr = n_valid / 8;               // a narrow operand: the row's first n_valid features
                             for (int c = threadIdx.x; c < TILE_ROWS * cpr; c += NUM_EPILOGUE) {
                                 const int r = c / cpr, k = c % cpr;
                                 const uint4 val = *reinterpret_cast<const uint4 *>(staging + r * (SLAB * NH * 2) + k * 16);
@@ -699,7 +703,7 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
                 } else if (!partial) {
 #pragma unroll
                     for (int h = 0; h < NH; ++h) {
-                        if (h * SLAB + 32 * q + lane >= prm.n_valid) continue;
+                        if (h * SLAB + 32 * q + lane >= n_valid) continue;
                         const int64_t base = (w * TILE_ROWS) * prm.ldc + h * SLAB + 32 * q + lane;
 #pragma unroll
                         for (int r = 0; r < 16; ++r)
@@ -738,7 +742,7 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
                         }
                         epilogue_sync();
                     }
-                    if (*reinterpret_cast<volatile int *>(&ss->last_piece)) sum_pieces<NH>(prm.partial, prm.N, prm.n_valid, prm.C, prm.ldc, prm.c_dtype, w, k0, k_last, q, lane);
+                    if (*reinterpret_cast<volatile int *>(&ss->last_piece)) sum_pieces<NH>(prm.partial, prm.N, n_valid, prm.C, prm.ldc, prm.c_dtype, w, k0, k_last, q, lane);
                 }
             }
             if (threadIdx.x == EPILOGUE_WARP0 * 32) prof_stamp<PROF>(prm.dbg, 5);      // last rows written
@@ -758,7 +762,7 @@ spmm_tc5_kernel(const Params prm, const __grid_constant__ CUtensorMap b_map) {
         const uint32_t gs = (uint32_t)(warp - PRODUCER_WARP0);
         // An operand of at most 64 features (one slab, NH = 1): only the first 64-feature half of a row
         // is fetched; the MMAs still multiply the whole slot, the other half's results are never read.
-        const bool narrow = NH == 1 && prm.n_valid <= 64;
+        const bool narrow = NARROW && n_valid <= 64;
         if (elect_one()) {
             constexpr uint32_t D = (uint32_t)C::kMetaDepth;
             const uint64_t keep = policy_keep(), stream_pol = policy_stream();
@@ -1019,8 +1023,12 @@ static long long g_wait_limit = WAIT_LIMIT_CYCLES;
 template <int NH>
 static cudaError_t opt_in_smem() {
     cudaError_t e = cudaFuncSetAttribute(spmm_tc5_kernel<NH, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<NH>::kSmem);
+    if (NH == 1 && e == cudaSuccess)
+        e = cudaFuncSetAttribute(spmm_tc5_kernel<1, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<1>::kSmem);
 #ifdef GRWS_TC5_PROFILING
     if (e == cudaSuccess) e = cudaFuncSetAttribute(spmm_tc5_kernel<NH, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<NH>::kSmem);
+    if (NH == 1 && e == cudaSuccess)
+        e = cudaFuncSetAttribute(spmm_tc5_kernel<1, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<1>::kSmem);
 #endif
     return e;
 }
@@ -1064,7 +1072,7 @@ __global__ void zero_words_kernel(int *p, int n) {
     for (int i = threadIdx.x; i < n; i += blockDim.x) p[i] = 0;
 }
 
-template <int NH, bool PROF>
+template <int NH, bool PROF, bool NARROW>
 static cudaError_t launch_dependent(const Params &prm, const CUtensorMap &b_map, int G, cudaStream_t stream) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)G);
@@ -1080,15 +1088,15 @@ static cudaError_t launch_dependent(const Params &prm, const CUtensorMap &b_map,
 #else
     cfg.numAttrs = 1;
 #endif
-    return cudaLaunchKernelEx(&cfg, spmm_tc5_kernel<NH, PROF>, prm, b_map);
+    return cudaLaunchKernelEx(&cfg, spmm_tc5_kernel<NH, PROF, NARROW>, prm, b_map);
 }
 
-template <int NH>
+template <int NH, bool NARROW = false>
 static cudaError_t launch_kernel(const Params &prm, const CUtensorMap &b_map, int G, cudaStream_t stream) {
 #ifdef GRWS_TC5_PROFILING
-    if (prm.dbg) return launch_dependent<NH, true>(prm, b_map, G, stream);
+    if (prm.dbg) return launch_dependent<NH, true, NARROW>(prm, b_map, G, stream);
 #endif
-    return launch_dependent<NH, false>(prm, b_map, G, stream);
+    return launch_dependent<NH, false, NARROW>(prm, b_map, G, stream);
 }
 
 // Tensor map of the dense operand for the row gathers: 2-D [K rows][N features], box of one row
@@ -1368,7 +1376,8 @@ int spmm_tc5_launch(const int64_t *window_offset, const int32_t *cols, const voi
         if (col0 == 0) zero_words_kernel<<<1, 256, 0, stream>>>(static_cast<int *>(scratch), (int)(STATUS_BYTES / sizeof(int)) + G);
         else zero_words_kernel<<<1, 256, 0, stream>>>(prm.split_count, G);
         GRWS_CUDA_TRY(cudaGetLastError());
-        GRWS_CUDA_TRY((pass_n == 128 ? launch_kernel<1>(prm, b_map, G, stream) : launch_kernel<2>(prm, b_map, G, stream)));
+        GRWS_CUDA_TRY((pass_n == 256 ? launch_kernel<2>(prm, b_map, G, stream)
+                       : prm.n_valid < 128 ? launch_kernel<1, true>(prm, b_map, G, stream) : launch_kernel<1>(prm, b_map, G, stream)));
         GRWS_CUDA_TRY(cudaGetLastError());
     }
     return GRWS_OK;
