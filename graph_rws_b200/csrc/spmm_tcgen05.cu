@@ -90,7 +90,7 @@ constexpr int64_t SPLIT256_OPERAND_BYTES = 8ll << 20;   // dense operand size ab
 #define GRWS_TC5_AUTO_MIN_N 16
 #endif
 #ifndef GRWS_TC5_AUTO_MIN_TILES
-#define GRWS_TC5_AUTO_MIN_TILES 32768
+#define GRWS_TC5_AUTO_MIN_TILES 512
 #endif
 constexpr int PLAN_MAGIC = 0x504c4e31;                                    // first word of a valid plan
 constexpr int PLAN_LONG_WINDOW_STAGES = 16;                               // planned ranges: a window of more stages may be split
@@ -1258,10 +1258,11 @@ bool spmm_tc5_supported(int dtype, int64_t N) {
     return (dtype == GRWS_F16 || dtype == GRWS_BF16) && (N == 256 || (N >= 8 && N <= 128 && N % 8 == 0));
 }
 
-// What GRWS_SPMM_AUTO picks the tcgen05 kernel for: widths 128 and 256 always; narrower operands when
-// the product is large (the kernel costs the same for every width up to 64 and up to 128, so it wins
-// by 25-35 % from 16 features on -- measured on a 114 M-entry graph and on a power-law graph of 2.5 M
-// entries -- but its fixed cost of ~20 us is above the warp-MMA kernel's on a small graph).
+// What GRWS_SPMM_AUTO picks the tcgen05 kernel for: widths 128 and 256 always; narrower operands from
+// 16 features and 512 tiles on (the kernel costs the same for every width up to 64 and up to 128, so
+// it wins by 25-35 % on large graphs -- measured on a 114 M-entry graph and on a power-law graph of
+// 2.5 M entries -- and the blocks of a sampled step, a few hundred to a few thousand tiles, take it
+// 10-13 us against 35-120 us on the warp-MMA kernel, whose few warps walk such a block serially).
 bool spmm_tc5_preferred(int dtype, int64_t N, int64_t num_tiles_bound) {
     if (!spmm_tc5_supported(dtype, N)) return false;
     return N >= 128 || (N >= GRWS_TC5_AUTO_MIN_N && num_tiles_bound >= GRWS_TC5_AUTO_MIN_TILES);

@@ -371,7 +371,10 @@ void spmm_warp_plan(int64_t num_tiles_bound, int64_t *n_items, int64_t *chunk, i
         sms = 148;
     const int64_t target_items = (int64_t)sms * 112;
     int64_t c = ceil_div(num_tiles_bound > 0 ? num_tiles_bound : 1, target_items);
-    if (c < 64) c = 64;
+    // at least 64 tiles per item, 16 for a small product: a warp walks its tiles one after the other
+    // (~0.5 us per tile), so a block of a thousand tiles wants a hundred warps, not sixteen
+    const int64_t c_min = num_tiles_bound <= 65536 ? 16 : 64;
+    if (c < c_min) c = c_min;
     c = (c + 1) & ~int64_t(1);
     *chunk = c;
     *long_window = 2 * c;

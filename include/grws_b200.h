@@ -62,7 +62,7 @@ int grws_version(void);
  *                     e.g. the allocated tile count of `cols`;
  *   val_dtype must equal b_dtype; N % 8 == 0; ldb, ldc in elements, rows 16-byte aligned;
  *   algo : GRWS_SPMM_AUTO takes the tcgen05 kernel for fp16 / bf16 operands of width 128 or 256,
- *          and of widths 16 .. 120 when num_tiles_bound >= 32768 (a narrow operand is multiplied
+ *          and of widths 16 .. 120 when num_tiles_bound >= 512 (a narrow operand is multiplied
  *          as 128 features of which the missing ones are zeros and only N are written); every
  *          other case runs on the warp-MMA kernel.  GRWS_SPMM_TCGEN05 accepts N = 256 and every
  *          multiple of 8 up to 128;
