@@ -298,7 +298,8 @@ def run_ours(args):
     # kernels of this library per step: the tcgen05 path is one launch per product (two for width
     # 256 above 8 MB of operand), the warp-MMA path a main kernel plus its fix-up kernel
     tc5 = args.algo != "warp" and dt in ("f16", "bf16") and width in (128, 256)
-    launches_per_step = 2 * ((2 if (width == 256 and csr.num_nodes * 512 > (8 << 20)) else 1) if tc5 else 2)
+    # (each tcgen05 launch follows a one-block kernel of this library that clears its status word and counters)
+    launches_per_step = 2 * ((4 if (width == 256 and csr.num_nodes * 512 > (8 << 20)) else 2) if tc5 else 2)
 
     # tile ranges of the CTAs: computed once per graph (what the layers do from the second product of
     # a graph on), or searched by every launch (--no-plan)
