@@ -812,6 +812,32 @@ def secondary_sampled(args, torch, scale=1.0, steps=10):
     barrier()
     core.check_device_status(device)
     step_ms = e0.elapsed_time(e1) / steps
+    # the same step with the sampler of batch n + 1 as a second branch of the graph that trains on batch n
+    serial_ms = None
+    if step_mode == "cuda graph" and not args.no_pipeline:
+        ok = 1
+        try:
+            pstep = graphed_sampled_step(model, sampler, topo, x_local, y, opt, per_gpu, fetch_rows=fetch, pipelined=True)
+            pstep.prime(seeds_for_step(), state["i"])
+        except Exception as exc:          # noqa: BLE001
+            sys.stderr.write(f"bench.py: pipelined sampled step not captured ({exc})\n")
+            ok = 0
+        if world > 1:
+            flag = torch.tensor([ok], device=device)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            ok = int(flag)
+        if ok:
+            for _ in range(2):
+                pstep(seeds_for_step(), state["i"])
+            barrier()
+            e0.record()
+            for _ in range(steps):
+                pstep(seeds_for_step(), state["i"])
+            e1.record()
+            barrier()
+            core.check_device_status(device)
+            serial_ms, step_ms = step_ms, e0.elapsed_time(e1) / steps
+            step_mode = "cuda graph, two branches: training on batch n, sampler of batch n + 1"
     # sampling + dedup + block build alone: CUDA events around `steps` fused calls
     for _ in range(2):
         sampler.sample_layers(topo, seeds_for_step())
@@ -830,14 +856,14 @@ def secondary_sampled(args, torch, scale=1.0, steps=10):
     n_dst, _, _ = core.sample_layers_sizes(per_gpu, fan, sampler.pad_to)
     sb = synthetic.sampling_algorithmic_bytes([c[3] for c in counts], [c[1] for c in counts], [c[2] for c in counts],
                                               [(d + 15) // 16 for d in n_dst], val_bytes=2)
-    t = torch.tensor([step_ms, samp_ms], dtype=torch.float64, device=device)
+    t = torch.tensor([step_ms, samp_ms, serial_ms or 0.0], dtype=torch.float64, device=device)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    step_ms, samp_ms = float(t[0]), float(t[1])
+    step_ms, samp_ms, serial_ms = float(t[0]), float(t[1]), (float(t[2]) if serial_ms else None)
     peak, peak_kind = measured_peaks()
     achieved = sb["total"] / (samp_ms * 1e-3) / 1e9
     out = {"metric": "sampled seeds/s (sample + build + 3-layer GCN step)", "seeds_per_s": world * per_gpu / (step_ms * 1e-3),
-           "ms_per_step": step_ms, "step_mode": step_mode, "sampling_only_seeds_per_s": world * per_gpu / (samp_ms * 1e-3), "sampling_ms": samp_ms,
+           "ms_per_step": step_ms, "step_mode": step_mode, "ms_per_step_one_branch": serial_ms, "sampling_only_seeds_per_s": world * per_gpu / (samp_ms * 1e-3), "sampling_ms": samp_ms,
            "n": world, "scaling": "weak", "scale": scale, "nodes": n, "nnz": nnz, "fanouts": [15, 10, 5], "seeds_per_gpu": per_gpu,
            "hidden": 256, "dtype": "f16", "topology": "CSR replicated per GPU, no full-graph BCSR",
            "features": feature_path,
@@ -913,6 +939,7 @@ def main():
     ap.add_argument("--no-secondary", action="store_true", help="SpMM line only")
     ap.add_argument("--no-plan", action="store_true", help="every SpMM launch searches its tile ranges (no per-graph plan)")
     ap.add_argument("--no-ref-gpu", action="store_true")
+    ap.add_argument("--no-pipeline", action="store_true", help="sampled step: sampler and training in one chain, not two branches")
     ap.add_argument("--eager", action="store_true", help="time an eager loop of steps instead of CUDA-graph replays")
     args = ap.parse_args()
     if args.workload in SECONDARY:

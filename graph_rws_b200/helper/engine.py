@@ -187,31 +187,99 @@ class GraphedStep:
         return self.loss
 
 
-def graphed_sampled_step(model, sampler, graph, features, labels, optimizer, num_seeds, fetch_rows=None, warmup=3):
-    """``step(seeds, step_index) -> loss`` for sampled training, as one CUDA graph per step."""
+def _block_tensors(blocks):
+    """The device arrays of a list of sampled blocks, each once (a hop's input nodes may be the next
+    hop's output nodes)."""
+    seen, out = set(), []
+    for b in blocks:
+        for t in (b.window_offset, b.original_col_indices, b.values_condensed, b.output_nodes, b.input_nodes):
+            if t.data_ptr() not in seen:
+                seen.add(t.data_ptr())
+                out.append(t)
+    return out
+
+
+def graphed_sampled_step(model, sampler, graph, features, labels, optimizer, num_seeds, fetch_rows=None, warmup=3,
+                         pipelined=False):
+    """``step(seeds, step_index) -> loss`` for sampled training, as one CUDA graph per step.
+
+    ``pipelined=True`` overlaps the sampler with the training: the graph of a step has two branches,
+    one trains on the blocks sampled during the previous step, the other samples and builds the
+    blocks for the seeds passed to this call (the reference overlaps the two with a producer thread
+    and a side stream, helper/engine.py:196-260; here both are branches of one graph launch, so the
+    GPU runs the sampler's small kernels in the gaps of the training's).  ``step`` then returns the
+    loss of the batch given to the PREVIOUS call; ``step.prime(seeds, step_index)`` samples the
+    first batch.  Results per batch are the same as without pipelining: sampling depends on the
+    seeds and the step index only."""
     device = labels.device
     seeds_buf = torch.zeros(num_seeds, dtype=torch.int32, device=device)
     seed_dev = torch.zeros(1, dtype=torch.int64, device=device)          # the Philox seed, read by the sampling kernels
+    model.train()
 
-    def body():
-        blocks, x = layer0_inputs(sampler.sample_layers(graph, seeds_buf, seed_dev=seed_dev), features, fetch_rows)
+    def train_on(blocks, seeds):
+        blocks, x = layer0_inputs(blocks, features, fetch_rows)
         _zero_grads(model, optimizer)
         logits = model(blocks, x)[:num_seeds]
-        loss = F.cross_entropy(logits.float(), labels[seeds_buf.long()])
+        loss = F.cross_entropy(logits.float(), labels[seeds.long()])
         loss.backward()
         _allreduce_grads(model)
         torch.nn.utils.clip_grad_norm_(model.parameters(), max_norm=1.0)
         optimizer.step()
         return loss.detach()
 
-    model.train()
+    if not pipelined:
+        def body():
+            return train_on(sampler.sample_layers(graph, seeds_buf, seed_dev=seed_dev), seeds_buf)
+
+        graphed = GraphedStep(body, device, warmup)
+
+        def step(seeds, step_index=0):
+            seeds_buf.copy_(seeds, non_blocking=True)
+            seed_dev.fill_(int(sampler.seed) + int(step_index))
+            return graphed.replay()
+        step.graphed = graphed
+        return step
+
+    # the batch being trained on lives in arrays of its own, outside the graph's memory pool; the
+    # sampler branch fills fresh arrays, which are copied over once both branches are done
+    seeds_cur = torch.zeros(num_seeds, dtype=torch.int32, device=device)
+    blocks_cur = sampler.sample_layers(graph, seeds_cur, seed_dev=seed_dev)
+    cur_tensors = _block_tensors(blocks_cur)
+    side = torch.cuda.Stream(device)
+    keep = {}
+
+    def body():
+        main = torch.cuda.current_stream(device)
+        side.wait_stream(main)
+        with torch.cuda.stream(side):
+            blocks_next = sampler.sample_layers(graph, seeds_buf, seed_dev=seed_dev)
+        for b in blocks_cur:
+            b._shared.clear()                  # transposed blocks of the previous batch
+        loss = train_on(blocks_cur, seeds_cur)
+        main.wait_stream(side)
+        nxt = _block_tensors(blocks_next)
+        assert len(nxt) == len(cur_tensors)
+        for dst, src in zip(cur_tensors, nxt):
+            dst.copy_(src)
+        seeds_cur.copy_(seeds_buf)
+        keep['next'] = blocks_next             # the sampler branch's arrays stay allocated as long as the graph
+        return loss
+
     graphed = GraphedStep(body, device, warmup)
+
+    def prime(seeds, step_index=0):
+        seeds_cur.copy_(seeds, non_blocking=True)
+        seed_dev.fill_(int(sampler.seed) + int(step_index))
+        first = sampler.sample_layers(graph, seeds_cur, seed_dev=seed_dev)
+        for dst, src in zip(cur_tensors, _block_tensors(first)):
+            dst.copy_(src)
 
     def step(seeds, step_index=0):
         seeds_buf.copy_(seeds, non_blocking=True)
         seed_dev.fill_(int(sampler.seed) + int(step_index))
         return graphed.replay()
     step.graphed = graphed
+    step.prime = prime
     return step
 
 

@@ -232,3 +232,40 @@ def test_first_block_with_global_ids_equals_gathered_rows(graph):
     torch.testing.assert_close(out[0][0], out[1][0], rtol=1e-2, atol=1e-2)
     for a, b in zip(out[0][1], out[1][1]):
         torch.testing.assert_close(a, b, rtol=2e-2, atol=2e-2)
+
+
+def test_two_branch_graph_step_trains_like_the_one_chain_graph_step(graph):
+    """helper.graphed_sampled_step: with ``pipelined=True`` the sampler of the next batch runs as a
+    second branch of the graph that trains on the current one.  Batch by batch the losses are those
+    of the one-chain graph (sampling depends on seeds and step index only), one call later."""
+    import copy
+    from graph_rws_b200 import GCN_BCSR
+    from graph_rws_b200.data import CSRTopology
+    from graph_rws_b200.helper import graphed_sampled_step
+    from graph_rws_b200.sampler import BCSRSampler
+    dev = torch.device("cuda")
+    n = graph.num_nodes
+    topo = CSRTopology(*_dev_csr(graph), block_dtype=torch.float16)
+    x = torch.randn(n, 128, generator=torch.Generator().manual_seed(3)).half().to(dev)
+    y = torch.randint(0, 7, (n,), generator=torch.Generator().manual_seed(4)).to(dev)
+    torch.manual_seed(6)
+    base = GCN_BCSR(128, 128, 7, num_layers=3, dropout=0.0, use_checkpoint=False).to(dev).half()
+    batches = [((torch.arange(256) * 7 + 3 + 11 * i) % n).to(torch.int32).to(dev) for i in range(5)]
+    losses = {}
+    for mode in ("chain", "branches"):
+        model = copy.deepcopy(base)
+        opt = torch.optim.Adam(model.parameters(), lr=1e-3, eps=1e-4, capturable=True)
+        sampler = BCSRSampler([5, 4, 3], verbose=False, seed=3, pad_to=256)
+        step = graphed_sampled_step(model, sampler, topo, x, y, opt, 256, pipelined=(mode == "branches"))
+        out = []
+        if mode == "chain":
+            for i, b in enumerate(batches[:4]):
+                out.append(float(step(b, i)))
+        else:
+            step.prime(batches[0], 0)
+            for i in range(1, 5):
+                out.append(float(step(batches[i], i)))      # the loss of batch i - 1
+        losses[mode] = out
+    torch.cuda.synchronize()
+    assert all(np.isfinite(losses["chain"]))
+    np.testing.assert_allclose(losses["branches"], losses["chain"], rtol=2e-3, atol=2e-3)
