@@ -645,7 +645,7 @@ def secondary_gcn_full(args, torch, scale=1.0, steps=10):
     y = torch.randint(0, 41, (n,), generator=gen, device=device)
     train = torch.randperm(n, generator=gen, device=device)[:n // 2].sort().values
     model = GCN_BCSR(608, 256, 41, num_layers=2, dropout=0.5, use_checkpoint=False).to(device).bfloat16()
-    opt = torch.optim.Adam(model.parameters(), lr=1e-3, eps=1e-4, capturable=not args.eager)
+    opt = torch.optim.Adam(model.parameters(), lr=1e-3, eps=1e-4, capturable=not args.eager, fused=True)
     tiles = int(graph.window_offset[-1])
     step_args = None
     if world == 1:
@@ -758,7 +758,7 @@ def secondary_sampled(args, torch, scale=1.0, steps=10):
     if world > 1:
         for p_ in model.parameters():
             dist.broadcast(p_.data, 0)
-    opt = torch.optim.Adam(model.parameters(), lr=1e-3, eps=1e-4, capturable=not args.eager)
+    opt = torch.optim.Adam(model.parameters(), lr=1e-3, eps=1e-4, capturable=not args.eager, fused=True)
     sampler = BCSRSampler([15, 10, 5], verbose=False, pad_to=256)          # fused: one call per step, no read-backs
     per_gpu = 1024
     state = {"i": 0}

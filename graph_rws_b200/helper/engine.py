@@ -188,14 +188,16 @@ class GraphedStep:
 
 
 def _block_tensors(blocks):
-    """The device arrays of a list of sampled blocks, each once (a hop's input nodes may be the next
-    hop's output nodes)."""
+    """The device allocations behind a list of sampled blocks, each once: the fused sampler carves a
+    step's arrays out of three allocations (ids, values, offsets), so copying a batch is a handful
+    of large copies rather than one per array."""
     seen, out = set(), []
     for b in blocks:
         for t in (b.window_offset, b.original_col_indices, b.values_condensed, b.output_nodes, b.input_nodes):
-            if t.data_ptr() not in seen:
-                seen.add(t.data_ptr())
-                out.append(t)
+            base = t._base if t._base is not None else t
+            if base.data_ptr() not in seen:
+                seen.add(base.data_ptr())
+                out.append(base)
     return out
 
 
