@@ -160,7 +160,7 @@ def spmm_tc(window_offset, original_col_indices, values_condensed, input_B, warp
 # CSR -> BCSR and the cached transposed BCSR
 # ---------------------------------------------------------------------------------------------
 def csr_to_bcsr(num_rows, row_ptr, col_idx, values, tile_rows=16, tile_cols=8, values_dtype=torch.float32,
-                exact=True, nnz_is_bound=False):
+                exact=True, nnz_is_bound=False, num_cols=0):
     """Device builder: CUDA tensors in, CUDA tensors out (window_offset, cols, vals).
 
     With ``exact`` the tile count is read back from the device to size ``cols`` / ``vals`` exactly
@@ -169,7 +169,8 @@ def csr_to_bcsr(num_rows, row_ptr, col_idx, values, tile_rows=16, tile_cols=8, v
     arrays then end in unused tiles (column ids -1, values 0) which no kernel visits, since all of
     them walk ``window_offset``.  Per-step builders (sampled blocks, their transposes) use it.
     ``nnz_is_bound``: only the first ``row_ptr[num_rows]`` entries of ``col_idx`` / ``values`` exist,
-    their length is a bound (the caller did not read the count back either)."""
+    their length is a bound (the caller did not read the count back either); ``num_cols`` (with
+    ``nnz_is_bound``): every column id is below it, which lets the builder sort narrower keys."""
     if tile_rows != 16 or tile_cols != 8:
         raise RuntimeError("Currently only supports tile 16x8")
     lib = _native.lib()
@@ -182,9 +183,13 @@ def csr_to_bcsr(num_rows, row_ptr, col_idx, values, tile_rows=16, tile_cols=8, v
     wo = torch.empty(W + 1, dtype=torch.int64, device=dev)
     scratch = _scratch(lib.grws_csr_to_bcsr_scratch_bytes(num_rows, nnz), dev)
     st = _stream(dev)
-    count = lib.grws_csr_to_bcsr_count_bounded if nnz_is_bound else lib.grws_csr_to_bcsr_count
-    _native.check(count(num_rows, _ptr(row_ptr), _ptr(col_idx), _ptr(values), nnz,
-                        wo.data_ptr(), scratch.data_ptr(), scratch.numel(), st))
+    if nnz_is_bound:
+        _native.check(lib.grws_csr_to_bcsr_count_bounded(num_rows, _ptr(row_ptr), _ptr(col_idx), _ptr(values), nnz,
+                                                         int(num_cols), wo.data_ptr(), scratch.data_ptr(),
+                                                         scratch.numel(), st))
+    else:
+        _native.check(lib.grws_csr_to_bcsr_count(num_rows, _ptr(row_ptr), _ptr(col_idx), _ptr(values), nnz,
+                                                 wo.data_ptr(), scratch.data_ptr(), scratch.numel(), st))
     T = int(wo[-1].item()) if exact else nnz // 8 + W
     cols = torch.empty(T * 8, dtype=torch.int32, device=dev)
     vals = torch.empty(T * 128, dtype=values_dtype, device=dev)
@@ -225,7 +230,7 @@ def bcsr_transpose(window_offset, cols, vals, num_cols, values_dtype=None, exact
                                                W, num_cols, row_ptr_t.data_ptr(), _ptr(col_t), _ptr(val_t),
                                                scratch.data_ptr(), scratch.numel(), st))
     return csr_to_bcsr(num_cols, row_ptr_t, col_t, val_t, values_dtype=values_dtype or vals.dtype, exact=exact,
-                       nnz_is_bound=nnz_bound is not None)
+                       nnz_is_bound=nnz_bound is not None, num_cols=W * 16)
 
 
 class _TransposeCache:

@@ -36,8 +36,8 @@ SIGNATURES = {
     "grws_csr_to_bcsr_scratch_bytes": (c_sz, [c_i64, c_i64]),
     "grws_csr_to_bcsr_count": (c_i32, [c_i64, c_vp, c_vp, c_vp, c_i64, c_vp, c_vp, c_sz, c_vp]),
     "grws_csr_to_bcsr_fill": (c_i32, [c_i64, c_i64, c_vp, c_i64, c_vp, c_vp, c_i32, c_vp, c_sz, c_vp]),
-    "grws_csr_to_bcsr_count_bounded": (c_i32, [c_i64, c_vp, c_vp, c_vp, c_i64, c_vp, c_vp, c_sz, c_vp]),
-    "grws_block_build_count": (c_i32, [c_vp, c_vp, c_i64, c_i32, c_vp, c_vp, c_sz, c_vp]),
+    "grws_csr_to_bcsr_count_bounded": (c_i32, [c_i64, c_vp, c_vp, c_vp, c_i64, c_i64, c_vp, c_vp, c_sz, c_vp]),
+    "grws_block_build_count": (c_i32, [c_vp, c_vp, c_i64, c_i32, c_i64, c_vp, c_vp, c_sz, c_vp]),
     "grws_bcsr_transpose_scratch_bytes": (c_sz, [c_i64]),
     "grws_bcsr_transpose_count": (c_i32, [c_vp, c_vp, c_vp, c_i32, c_i64, c_i64, c_vp, c_vp, c_sz, c_vp]),
     "grws_bcsr_transpose_fill": (c_i32, [c_vp, c_vp, c_vp, c_i32, c_i64, c_i64, c_vp, c_vp, c_vp,

@@ -36,6 +36,7 @@ struct BuildScratch {
     int32_t *nuniq;         // [W+2] unique columns per window
     int32_t *ufirst;        // [W+2] exclusive scan of nuniq
     int64_t *tiles;         // [W+2] tiles per window, shifted by one
+    int32_t *col_bits;      // bits of the column field of the keys (the count phase leaves it for the fill phase)
     void *cub_tmp;
     size_t cub_bytes;
     size_t total;
@@ -66,46 +67,62 @@ static BuildScratch carve(void *base, int64_t nnz, int64_t W) {
     s.nuniq = (int32_t *)take((size_t)(W + 2) * 4);
     s.ufirst = (int32_t *)take((size_t)(W + 2) * 4);
     s.tiles = (int64_t *)take((size_t)(W + 2) * 8);
+    s.col_bits = (int32_t *)take(64);
     s.cub_bytes = cub_temp_bytes(nnz, W);
     s.cub_tmp = take(s.cub_bytes);
     s.total = off;
     return s;
 }
 
+// Sort key of an entry: window | column | row-in-window.  The column field has as many bits as the
+// caller's bound on the column ids needs (32 without a bound), so that the radix sort, which runs one
+// pass per 8 key bits, has fewer passes to make: the blocks of a sampled step have 2^13 windows and 2^21
+// columns at most, 38 key bits instead of 49.  A column field of b bits holds ids below 2^b - 1 only,
+// which keeps the invalid key (all ones) apart from every real key within the sorted bits.
+__host__ __device__ __forceinline__ uint64_t make_key(int64_t row, int32_t col, int col_bits) {
+    return ((uint64_t)(row / TILE_ROWS) << (col_bits + ROW_BITS)) | ((uint64_t)(uint32_t)col << ROW_BITS) | (uint64_t)(row % TILE_ROWS);
+}
+
+static int column_bits(int64_t num_cols_bound) {
+    if (num_cols_bound <= 0 || num_cols_bound >= (1LL << 31)) return 32;
+    int b = 0;
+    for (int64_t x = num_cols_bound; x > 0; x >>= 1) ++b;      // ids < bound <= 2^b - 1
+    return b;
+}
+
 __global__ void make_keys_kernel(int64_t num_rows, const int64_t *__restrict__ row_ptr,
-                                 const int32_t *__restrict__ col_idx, uint64_t *__restrict__ keys) {
+                                 const int32_t *__restrict__ col_idx, uint64_t *__restrict__ keys, int col_bits) {
     // one warp per row
     const int64_t row = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
     if (row >= num_rows) return;
     const int64_t e0 = row_ptr[row], e1 = row_ptr[row + 1];
-    const uint64_t hi = ((uint64_t)(row / TILE_ROWS) << (32 + ROW_BITS));
-    const uint64_t lo = (uint64_t)(row % TILE_ROWS);
     for (int64_t e = e0 + lane; e < e1; e += 32)
-        keys[e] = hi | ((uint64_t)(uint32_t)col_idx[e] << ROW_BITS) | lo;
+        keys[e] = make_key(row, col_idx[e], col_bits);
 }
 
 // keys of a hop's fixed-stride neighbour lists: entry (row i, slot j) holds local column id
 // local[i * fanout + j], or -1 when the slot is empty
 __global__ void make_keys_lists_kernel(int64_t n_entries, int fanout, const int32_t *__restrict__ local,
-                                       uint64_t *__restrict__ keys) {
+                                       uint64_t *__restrict__ keys, int col_bits) {
     const int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (e >= n_entries) return;
     const int32_t c = local[e];
     const int64_t row = e / fanout;
-    keys[e] = c < 0 ? INVALID_KEY
-                    : (((uint64_t)(row / TILE_ROWS) << (32 + ROW_BITS)) | ((uint64_t)(uint32_t)c << ROW_BITS) | (uint64_t)(row % TILE_ROWS));
+    keys[e] = c < 0 ? INVALID_KEY : make_key(row, c, col_bits);
 }
 
 __global__ void head_flags_kernel(int64_t nnz, const uint64_t *__restrict__ keys,
-                                  int32_t *__restrict__ flags, int32_t *__restrict__ nuniq) {
+                                  int32_t *__restrict__ flags, int32_t *__restrict__ nuniq, int col_bits,
+                                  int32_t *__restrict__ col_bits_out) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= nnz) return;
+    if (i == 0) *col_bits_out = col_bits;                  // the fill phase decodes the keys with it
     if (keys[i] == INVALID_KEY) { flags[i] = 0; return; }
     const uint64_t k = keys[i] >> ROW_BITS;
     const bool head = (i == 0) || ((keys[i - 1] >> ROW_BITS) != k);
     flags[i] = head ? 1 : 0;
-    if (head) atomicAdd(nuniq + (k >> 32), 1);
+    if (head) atomicAdd(nuniq + (k >> col_bits), 1);
 }
 
 __global__ void tiles_kernel(int64_t W, const int32_t *__restrict__ nuniq, int64_t *__restrict__ tiles) {
@@ -123,14 +140,15 @@ template <typename T>
 __global__ void fill_kernel(int64_t nnz, const uint64_t *__restrict__ keys, const float *__restrict__ vals,
                             const int32_t *__restrict__ uidx, const int32_t *__restrict__ ufirst,
                             const int64_t *__restrict__ window_offset, int32_t *__restrict__ out_cols,
-                            T *__restrict__ out_vals) {
+                            T *__restrict__ out_vals, const int32_t *__restrict__ col_bits_in) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= nnz) return;
     const uint64_t key = keys[i];
     if (key == INVALID_KEY) return;
     if (i + 1 < nnz && keys[i + 1] == key) return;          // an identical (row, column) follows: it wins
-    const int64_t w = (int64_t)(key >> (32 + ROW_BITS));
-    const int32_t col = (int32_t)((key >> ROW_BITS) & 0xffffffffu);
+    const int col_bits = *col_bits_in;
+    const int64_t w = (int64_t)(key >> (col_bits + ROW_BITS));
+    const int32_t col = (int32_t)((key >> ROW_BITS) & ((1ull << col_bits) - 1ull));
     const int r = (int)(key & (TILE_ROWS - 1));
     const int32_t slot = uidx[i] - 1 - ufirst[w];
     const int64_t tile = window_offset[w] + slot / TILE_COLS;
@@ -219,18 +237,18 @@ using namespace grws;
 // keys in s.keys_a (values alongside), flags the first entry of every (window, column) run and
 // turns the unique-column counts into window_offset.
 static int count_from_keys(const BuildScratch &s, int64_t nnz, int64_t W, const float *values,
-                           int64_t *window_offset, cudaStream_t st) {
+                           int64_t *window_offset, int col_bits, cudaStream_t st) {
     GRWS_CUDA_TRY(cudaMemsetAsync(s.nuniq, 0, (size_t)(W + 2) * 4, st));
     if (nnz > 0) {
         size_t tmp = s.cub_bytes;
         // only the bits a key can use are sorted; the invalid key is all ones there too, so it
-        // still sorts behind every real key (no column id is 0xffffffff)
-        int end_bit = 32 + ROW_BITS;
+        // still sorts behind every real key (no column id fills its field with ones)
+        int end_bit = col_bits + ROW_BITS;
         for (int64_t x = W; x > 0; x >>= 1) ++end_bit;
         if (end_bit > 64) end_bit = 64;
         GRWS_CUDA_TRY(cub::DeviceRadixSort::SortPairs(s.cub_tmp, tmp, s.keys_a, s.keys_b, values, s.vals_b,
                                                       (int)nnz, 0, end_bit, st));
-        head_flags_kernel<<<blocks_for(nnz, 256), 256, 0, st>>>(nnz, s.keys_b, s.flags, s.nuniq);
+        head_flags_kernel<<<blocks_for(nnz, 256), 256, 0, st>>>(nnz, s.keys_b, s.flags, s.nuniq, col_bits, s.col_bits);
         tmp = s.cub_bytes;
         GRWS_CUDA_TRY(cub::DeviceScan::InclusiveSum(s.cub_tmp, tmp, s.flags, s.uidx, (int)nnz, st));
     }
@@ -268,8 +286,8 @@ size_t grws_csr_to_bcsr_scratch_bytes(int64_t num_rows, int64_t nnz) {
 }
 
 static int csr_count(int64_t num_rows, const int64_t *row_ptr, const int32_t *col_idx, const float *values,
-                     int64_t nnz, bool nnz_is_bound, int64_t *window_offset, void *scratch, size_t scratch_bytes,
-                     void *stream) {
+                     int64_t nnz, bool nnz_is_bound, int64_t num_cols_bound, int64_t *window_offset, void *scratch,
+                     size_t scratch_bytes, void *stream) {
     GRWS_REQUIRE(num_rows >= 0 && nnz >= 0, "negative size");
     GRWS_REQUIRE(nnz < 0x7fffffffLL, "csr_to_bcsr handles fewer than 2^31 entries");
     const int64_t W = ceil_div(num_rows, TILE_ROWS);
@@ -279,32 +297,35 @@ static int csr_count(int64_t num_rows, const int64_t *row_ptr, const int32_t *co
     BuildScratch s = carve(scratch, nnz, W);
     if (scratch_bytes < s.total) return fail(GRWS_ERR_SCRATCH, "csr_to_bcsr scratch too small: %zu < %zu", scratch_bytes, s.total);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int col_bits = column_bits(num_cols_bound);
     if (nnz > 0) {
         // entries of the arrays past row_ptr[num_rows] (a CSR sized by a bound) keep the invalid key
         if (nnz_is_bound) GRWS_CUDA_TRY(cudaMemsetAsync(s.keys_a, 0xff, (size_t)nnz * 8, st));
-        make_keys_kernel<<<blocks_for(num_rows * 32, 256), 256, 0, st>>>(num_rows, row_ptr, col_idx, s.keys_a);
+        make_keys_kernel<<<blocks_for(num_rows * 32, 256), 256, 0, st>>>(num_rows, row_ptr, col_idx, s.keys_a, col_bits);
     }
-    return count_from_keys(s, nnz, W, values, window_offset, st);
+    return count_from_keys(s, nnz, W, values, window_offset, col_bits, st);
 }
 
 __attribute__((visibility("default")))
 int grws_csr_to_bcsr_count(int64_t num_rows, const int64_t *row_ptr, const int32_t *col_idx,
                            const float *values, int64_t nnz, int64_t *window_offset, void *scratch,
                            size_t scratch_bytes, void *stream) {
-    return csr_count(num_rows, row_ptr, col_idx, values, nnz, false, window_offset, scratch, scratch_bytes, stream);
+    return csr_count(num_rows, row_ptr, col_idx, values, nnz, false, 0, window_offset, scratch, scratch_bytes, stream);
 }
 
 __attribute__((visibility("default")))
 int grws_csr_to_bcsr_count_bounded(int64_t num_rows, const int64_t *row_ptr, const int32_t *col_idx,
-                                   const float *values, int64_t nnz_bound, int64_t *window_offset, void *scratch,
-                                   size_t scratch_bytes, void *stream) {
-    return csr_count(num_rows, row_ptr, col_idx, values, nnz_bound, true, window_offset, scratch, scratch_bytes, stream);
+                                   const float *values, int64_t nnz_bound, int64_t num_cols_bound,
+                                   int64_t *window_offset, void *scratch, size_t scratch_bytes, void *stream) {
+    GRWS_REQUIRE(num_cols_bound >= 0, "negative size");
+    return csr_count(num_rows, row_ptr, col_idx, values, nnz_bound, true, num_cols_bound, window_offset, scratch, scratch_bytes,
+                     stream);
 }
 
 __attribute__((visibility("default")))
-int grws_block_build_count(const int32_t *local, const float *w, int64_t n_dst, int fanout, int64_t *window_offset,
-                           void *scratch, size_t scratch_bytes, void *stream) {
-    GRWS_REQUIRE(n_dst >= 0 && fanout > 0, "bad size");
+int grws_block_build_count(const int32_t *local, const float *w, int64_t n_dst, int fanout, int64_t num_cols_bound,
+                           int64_t *window_offset, void *scratch, size_t scratch_bytes, void *stream) {
+    GRWS_REQUIRE(n_dst >= 0 && fanout > 0 && num_cols_bound >= 0, "bad size");
     const int64_t n_entries = n_dst * fanout;
     GRWS_REQUIRE(n_entries < 0x7fffffffLL, "hop too large");
     const int64_t W = ceil_div(n_dst, TILE_ROWS);
@@ -312,9 +333,10 @@ int grws_block_build_count(const int32_t *local, const float *w, int64_t n_dst, 
     BuildScratch s = carve(scratch, n_entries, W);
     if (scratch_bytes < s.total) return fail(GRWS_ERR_SCRATCH, "block build scratch too small: %zu < %zu", scratch_bytes, s.total);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int col_bits = column_bits(num_cols_bound);
     if (n_entries > 0)
-        make_keys_lists_kernel<<<blocks_for(n_entries, 256), 256, 0, st>>>(n_entries, fanout, local, s.keys_a);
-    return count_from_keys(s, n_entries, W, w, window_offset, st);
+        make_keys_lists_kernel<<<blocks_for(n_entries, 256), 256, 0, st>>>(n_entries, fanout, local, s.keys_a, col_bits);
+    return count_from_keys(s, n_entries, W, w, window_offset, col_bits, st);
 }
 
 __attribute__((visibility("default")))
@@ -334,11 +356,11 @@ int grws_csr_to_bcsr_fill(int64_t num_rows, int64_t nnz, const int64_t *window_o
     if (nnz > 0) {
         const unsigned nb = blocks_for(nnz, 256);
         if (val_dtype == GRWS_F32)
-            fill_kernel<float><<<nb, 256, 0, st>>>(nnz, s.keys_b, s.vals_b, s.uidx, s.ufirst, window_offset, out_cols, (float *)out_vals);
+            fill_kernel<float><<<nb, 256, 0, st>>>(nnz, s.keys_b, s.vals_b, s.uidx, s.ufirst, window_offset, out_cols, (float *)out_vals, s.col_bits);
         else if (val_dtype == GRWS_F16)
-            fill_kernel<__half><<<nb, 256, 0, st>>>(nnz, s.keys_b, s.vals_b, s.uidx, s.ufirst, window_offset, out_cols, (__half *)out_vals);
+            fill_kernel<__half><<<nb, 256, 0, st>>>(nnz, s.keys_b, s.vals_b, s.uidx, s.ufirst, window_offset, out_cols, (__half *)out_vals, s.col_bits);
         else if (val_dtype == GRWS_BF16)
-            fill_kernel<__nv_bfloat16><<<nb, 256, 0, st>>>(nnz, s.keys_b, s.vals_b, s.uidx, s.ufirst, window_offset, out_cols, (__nv_bfloat16 *)out_vals);
+            fill_kernel<__nv_bfloat16><<<nb, 256, 0, st>>>(nnz, s.keys_b, s.vals_b, s.uidx, s.ufirst, window_offset, out_cols, (__nv_bfloat16 *)out_vals, s.col_bits);
         else
             return fail(GRWS_ERR_UNSUPPORTED, "bad value dtype %d", val_dtype);
     }

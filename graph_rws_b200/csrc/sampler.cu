@@ -429,8 +429,8 @@ int grws_sample_layers_sizes(int64_t num_seeds, const int *fanouts, int num_hops
 
 // builder scratch, defined in bcsr_build.cu
 size_t grws_csr_to_bcsr_scratch_bytes(int64_t num_rows, int64_t nnz);
-int grws_block_build_count(const int32_t *local, const float *w, int64_t n_dst, int fanout, int64_t *window_offset,
-                           void *scratch, size_t scratch_bytes, void *stream);
+int grws_block_build_count(const int32_t *local, const float *w, int64_t n_dst, int fanout, int64_t num_cols_bound,
+                           int64_t *window_offset, void *scratch, size_t scratch_bytes, void *stream);
 int grws_csr_to_bcsr_fill(int64_t num_rows, int64_t nnz, const int64_t *window_offset, int64_t num_tiles,
                           int32_t *out_cols, void *out_vals, int val_dtype, void *scratch, size_t scratch_bytes,
                           void *stream);
@@ -518,7 +518,7 @@ int grws_sample_layers(const int64_t *row_ptr, const int32_t *col_idx, const flo
         rank_new_kernel<<<nblocks(n_entries, 256), 256, 0, st>>>(d.cand_sorted, d.n_new, nd, d.keys, d.vals, mask, out_src[h]);
         localize_flat_kernel<<<nblocks(n_entries, 256), 256, 0, st>>>(s.nbr, n_entries, d.keys, d.vals, mask, s.local);
         // 3. the hop's BCSR block straight from the fixed-stride lists
-        if (int e = grws_block_build_count(s.local, s.w, nd, (int)f, out_window_offset[h], s.build, s.build_bytes, stream)) return e;
+        if (int e = grws_block_build_count(s.local, s.w, nd, (int)f, n_src[h], out_window_offset[h], s.build, s.build_bytes, stream)) return e;
         if (int e = grws_csr_to_bcsr_fill(nd, n_entries, out_window_offset[h], tiles[h], out_cols[h], out_vals[h], val_dtype,
                                           s.build, s.build_bytes, stream)) return e;
         if (out_counts)

@@ -188,18 +188,23 @@ int grws_csr_to_bcsr_fill(int64_t num_rows, int64_t nnz, const int64_t *window_o
 /* The count phase for CSR arrays whose entry count the host knows only as a bound (per-step
  * builders that must not read a size back): only the first row_ptr[num_rows] entries of col_idx
  * and values exist, nnz_bound >= that count sizes the scratch (grws_csr_to_bcsr_scratch_bytes(
- * num_rows, nnz_bound)) and is what grws_csr_to_bcsr_fill must be given as nnz. */
+ * num_rows, nnz_bound)) and is what grws_csr_to_bcsr_fill must be given as nnz.
+ * num_cols_bound: 0, or a number every column id is below; the builder then sorts keys with a
+ * narrower column field (fewer radix passes: it matters for the small blocks of a sampled step). */
 int grws_csr_to_bcsr_count_bounded(int64_t num_rows, const int64_t *row_ptr, const int32_t *col_idx,
-                                   const float *values, int64_t nnz_bound, int64_t *window_offset,
-                                   void *scratch, size_t scratch_bytes, void *stream);
+                                   const float *values, int64_t nnz_bound, int64_t num_cols_bound,
+                                   int64_t *window_offset, void *scratch, size_t scratch_bytes,
+                                   void *stream);
 
 /* The count phase straight from a hop's fixed-stride neighbour lists (this, with
  * grws_csr_to_bcsr_fill, replaces build_col_to_val_map_kernel + recompress_sampled_bcsr_kernel,
  * core/include/sampling.cuh:471-579,707-773): row i has the entries local[i*fanout + j] >= 0
  * with weights w[i*fanout + j]; -1 marks an empty slot.  Scratch as
- * grws_csr_to_bcsr_scratch_bytes(n_dst, n_dst*fanout); the fill call takes nnz = n_dst*fanout. */
+ * grws_csr_to_bcsr_scratch_bytes(n_dst, n_dst*fanout); the fill call takes nnz = n_dst*fanout.
+ * num_cols_bound as above (0, or the length of the hop's source list). */
 int grws_block_build_count(const int32_t *local, const float *w, int64_t n_dst, int fanout,
-                           int64_t *window_offset, void *scratch, size_t scratch_bytes, void *stream);
+                           int64_t num_cols_bound, int64_t *window_offset, void *scratch,
+                           size_t scratch_bytes, void *stream);
 
 /* ------------------------------------------------------------------------------------------
  * BCSR -> CSR of the transposed matrix (rows = the BCSR's column ids), the first half of
