@@ -27,6 +27,7 @@ from torch.utils.checkpoint import checkpoint
 from .. import core
 from ..data import BCSRGraph
 from ..layers import BCSRGraphConv
+from ..layers.norm import act_layer_norm
 
 _ACTIVATIONS = {'relu': F.relu, 'elu': F.elu, 'gelu': F.gelu}
 
@@ -162,9 +163,12 @@ class GCN_BCSR(nn.Module):
                 h_out = h_out + self._get_residual(l, g, prev_g, h_res, h_out.shape[0])
             h = h_out
             if l < len(self.layers) - 1:
-                h = self.activation(h)
                 if self.norms:
-                    h = self.norms[l](h)
+                    # activation and normalisation in one pass over the rows when the activation is ReLU
+                    relu = self.activation is F.relu
+                    h = act_layer_norm(h if relu else self.activation(h), self.norms[l], relu)
+                else:
+                    h = self.activation(h)
                 if self.dropout_layer is not None:
                     h = self.dropout_layer(h)
         return h
@@ -178,7 +182,9 @@ class GCN_BCSR(nn.Module):
         for l, layer in enumerate(self.layers):
             h = layer(g_copy, h)
             if l < len(self.layers) - 1:
-                h = self.activation(h)
                 if self.norms:
-                    h = self.norms[l](h)
+                    relu = self.activation is F.relu
+                    h = act_layer_norm(h if relu else self.activation(h), self.norms[l], relu)
+                else:
+                    h = self.activation(h)
         return h

@@ -207,6 +207,24 @@ int grws_block_build_count(const int32_t *local, const float *w, int64_t n_dst, 
                            size_t scratch_bytes, void *stream);
 
 /* ------------------------------------------------------------------------------------------
+ * Row normalisation between the graph convolutions: y = LayerNorm(act(x)) * gamma + beta over the
+ * C features of every row, act = identity or ReLU (relu_input != 0), and its backward pass.  The
+ * reference goes through torch.nn.LayerNorm and a separate activation (models/model.py:117-121).
+ * x, y, dy, dx: [rows, C] row-major and contiguous, gamma / beta [C], all of `dtype`; mean / rstd
+ * [rows] fp32 (written by the forward call, read by the backward call); dgamma / dbeta [C] fp32.
+ * C % 8 == 0, C <= 1024.  Deterministic (no atomics).  Backward scratch:
+ * grws_layer_norm_scratch_bytes(C).
+ * ------------------------------------------------------------------------------------------ */
+size_t grws_layer_norm_scratch_bytes(int64_t C);
+int grws_layer_norm_fwd(const void *x, const void *gamma, const void *beta, void *y, float *mean,
+                        float *rstd, int64_t rows, int64_t C, int dtype, int relu_input, float eps,
+                        void *stream);
+int grws_layer_norm_bwd(const void *x, const void *gamma, const void *dy, const float *mean,
+                        const float *rstd, void *dx, float *dgamma, float *dbeta, int64_t rows,
+                        int64_t C, int dtype, int relu_input, void *scratch, size_t scratch_bytes,
+                        void *stream);
+
+/* ------------------------------------------------------------------------------------------
  * BCSR -> CSR of the transposed matrix (rows = the BCSR's column ids), the first half of
  * building the cached transposed BCSR that the backward product runs on.  The reference has
  * no such structure: its backward is an atomicAdd scatter over the forward graph
