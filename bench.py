@@ -699,6 +699,8 @@ def secondary_gcn_full(args, torch, scale=1.0, steps=10):
     core.check_device_status(device)
     # the same epochs once more with events around every collective (untimed: the extra events and
     # the read-out serialise a little)
+    eager_step()                      # ranks arrive here at different times: one untimed epoch and a barrier align them
+    barrier()
     collective_timers.start()
     for _ in range(3):
         eager_step()
