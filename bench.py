@@ -714,9 +714,7 @@ def secondary_gcn_full(args, torch, scale=1.0, steps=10):
            "scale": scale, "nodes": n, "nnz": nnz, "tiles": tiles, "features": 602, "hidden": 256, "classes": 41, "dtype": "bf16",
            "all_gather_ms_per_epoch": float(ms[1]), "all_reduce_ms_per_epoch": float(ms[2]), "host_issue_ms_per_epoch": host_ms,
            "step_mode": step_mode,
-           "collective_ms_note": "cost of the collectives run one after the other, measured in separate epochs; in the timed "
-                                 "epochs the all-gather of a 256-wide operand goes in two 128-column halves, the second "
-                                 "under the first half's product",
+           "collective_ms_note": "measured in separate eager epochs with CUDA events around every collective",
            "parallelism": "rows x%d, all-gather of H / dY per layer, all-reduce of weight gradients" % world}
     del model, opt
     torch.cuda.empty_cache()

@@ -20,11 +20,6 @@ def _spmm_graph(graph, dense):
 
     A graph may bring its own product through a ``gather_dense`` hook: a row-sharded graph
     (parallel.RowShardedGraph) all-gathers the row shards of ``dense`` before its local product."""
-    pipelined = getattr(graph, 'gathered_product', None)
-    if pipelined is not None:
-        out = pipelined(dense)
-        if out is not None:
-            return out
     gather = getattr(graph, 'gather_dense', None)
     if gather is not None:
         dense = gather(dense)

@@ -227,38 +227,6 @@ class RowShardedGraph:
         # a product returns whole windows: rows past the rank's last row are padding
         return all_gather_rows_padded(dense_local[:self.num_rows], self.part, self.group)
 
-    def gathered_product(self, dense_local):
-        """``A_local @ all_gather(dense_local)``, or None when the plain route (``gather_dense`` then one
-        product) is to be taken.  An operand of 256 or more columns is exchanged and multiplied in
-        128-column slices: all slices' all-gathers are queued at once on the collective's stream and
-        each product starts when its slice has arrived, so every all-gather but the first runs
-        under the previous slice's product.  (The tcgen05 kernel multiplies a wide operand in
-        128-column passes anyway, so slicing costs the product nothing.)"""
-        n = dense_local.shape[1]
-        part = self.part
-        if (part.world == 1 or n < 256 or n % 128 or not dense_local.is_cuda or collective_timers.on
-                or dense_local.dtype not in (torch.float16, torch.bfloat16)):
-            return None
-        from .. import core
-        pad_rows, rows = part.max_rows(), self.num_rows
-        recvs, works = [], []
-        for c0 in range(0, n, 128):
-            send = torch.empty((pad_rows, 128), dtype=dense_local.dtype, device=dense_local.device)
-            send[:rows] = dense_local[:rows, c0:c0 + 128]
-            if rows < pad_rows:
-                send[rows:] = 0
-            recv = torch.empty((part.world * pad_rows, 128), dtype=dense_local.dtype, device=dense_local.device)
-            works.append(dist.all_gather_into_tensor(recv, send, group=self.group, async_op=True))
-            recvs.append(recv)
-        vals = self.local.values_as(dense_local.dtype)
-        out = torch.empty((self.num_windows * 16, n), dtype=dense_local.dtype, device=dense_local.device)
-        plan = self.local.spmm_plan(recvs[0].shape[0], 128)
-        for i, (recv, work) in enumerate(zip(recvs, works)):
-            work.wait()
-            core.spmm_raw(self.window_offset, self.original_col_indices, vals, recv, plan=plan,
-                          out=out[:, 128 * i:128 * (i + 1)])
-        return out
-
     def transposed(self, num_cols=None, dtype=None):
         if self._local_t is None:
             raise RuntimeError("this shard was built without its transposed rows")
