@@ -116,13 +116,26 @@ __global__ void head_flags_kernel(int64_t nnz, const uint64_t *__restrict__ keys
                                   int32_t *__restrict__ flags, int32_t *__restrict__ nuniq, int col_bits,
                                   int32_t *__restrict__ col_bits_out) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= nnz) return;
-    if (i == 0) *col_bits_out = col_bits;                  // the fill phase decodes the keys with it
-    if (keys[i] == INVALID_KEY) { flags[i] = 0; return; }
-    const uint64_t k = keys[i] >> ROW_BITS;
-    const bool head = (i == 0) || ((keys[i - 1] >> ROW_BITS) != k);
-    flags[i] = head ? 1 : 0;
-    if (head) atomicAdd(nuniq + (k >> col_bits), 1);
+    bool head = false;
+    uint64_t window = 0;
+    if (i < nnz) {
+        if (i == 0) *col_bits_out = col_bits;              // the fill phase decodes the keys with it
+        const uint64_t key = keys[i];
+        if (key != INVALID_KEY) {
+            const uint64_t k = key >> ROW_BITS;
+            head = (i == 0) || ((keys[i - 1] >> ROW_BITS) != k);
+            window = k >> col_bits;
+        }
+        flags[i] = head ? 1 : 0;
+    }
+    // The keys are sorted, so the heads a warp sees belong to one or two windows almost always: one
+    // atomic per window and warp instead of one per head (a window's counter otherwise takes
+    // hundreds of atomics from neighbouring threads).
+    const unsigned heads = __ballot_sync(0xffffffffu, head);
+    if (head) {
+        const unsigned same = __match_any_sync(heads, window);
+        if ((threadIdx.x & 31) == __ffs(same) - 1) atomicAdd(nuniq + window, __popc(same));
+    }
 }
 
 __global__ void tiles_kernel(int64_t W, const int32_t *__restrict__ nuniq, int64_t *__restrict__ tiles) {
