@@ -404,17 +404,14 @@ static int launch_warp(const SpmmWarpParams &prm, cudaStream_t stream) {
     const int64_t N = prm.N;
     dim3 block(WARPS_PER_CTA * 32);
     const unsigned gx = (unsigned)ceil_div(prm.n_items, WARPS_PER_CTA);
-    // features per warp: as many groups as keep the register budget (<= 128 features)
-    constexpr int kMaxGroups = 128 / G::kGroup;   // 2 (16-bit) or 4 (fp32)
+    // features per warp: at most two groups (128 features of a 16-bit type, 64 of fp32).  Four groups of
+    // fp32 need 202 registers, one CTA per SM: 584 us on the 2.5 M-entry graph against 375 us with two.
     if (N <= G::kGroup || narrow_slabs()) {
         const unsigned gy = (unsigned)ceil_div(N, G::kGroup);
         spmm_warp_kernel<DT, 1><<<dim3(gx, gy), block, 0, stream>>>(prm);
-    } else if (N <= 2 * G::kGroup || kMaxGroups == 2) {
+    } else {
         const unsigned gy = (unsigned)ceil_div(N, 2 * G::kGroup);
         spmm_warp_kernel<DT, 2><<<dim3(gx, gy), block, 0, stream>>>(prm);
-    } else {
-        const unsigned gy = (unsigned)ceil_div(N, kMaxGroups * G::kGroup);
-        spmm_warp_kernel<DT, kMaxGroups><<<dim3(gx, gy), block, 0, stream>>>(prm);
     }
     GRWS_CUDA_TRY(cudaGetLastError());
     if (prm.n_items > 1) {
