@@ -149,18 +149,19 @@ def test_planned_product_matches_oracle_with_split_windows(oracle, dt, N, out):
     assert torch.allclose(C.float(), C0.float(), rtol=2e-2, atol=2e-3)
 
 
+@pytest.mark.parametrize("N", [128, 256, 48])      # one slab; two slabs in one pass (one CTA per SM); the narrow variant
 @pytest.mark.parametrize("path", golden_cases(), ids=lambda p: p.split("bcsr_")[-1][:-4])
-def test_planned_product_on_golden_graphs(oracle, path):
+def test_planned_product_on_golden_graphs(oracle, path, N):
     from graph_rws_b200 import core
     dev = torch.device("cuda")
     c = load_case(path)
     wo, cols, vals = c["window_offset"], c["cols"], c["vals"]
     W, T = len(wo) - 1, int(wo[-1])
     K = int(max(int(cols.max()) + 1 if cols.size else 1, 16))
-    B = torch.randn(K, 128, generator=torch.Generator().manual_seed(9)).half()
+    B = torch.randn(K, N, generator=torch.Generator().manual_seed(9)).half()
     vals_t = torch.from_numpy(vals).half()
     wo_d = torch.from_numpy(wo).to(dev)
-    plan = core.spmm_plan(wo_d, T, K, 128)
+    plan = core.spmm_plan(wo_d, T, K, N)
     C = core.spmm_raw(wo_d, torch.from_numpy(cols).to(dev), vals_t.to(dev), B.to(dev), algo=core.ALGO_TCGEN05, check=True, plan=plan)
     C_ref = oracle.spmm_fwd(wo, cols, vals_t.float().numpy(), B.float().numpy())
     check_spmm_tolerance(C.float().cpu().numpy(), C_ref, None, "planned golden")
