@@ -269,3 +269,52 @@ def test_two_branch_graph_step_trains_like_the_one_chain_graph_step(graph):
     torch.cuda.synchronize()
     assert all(np.isfinite(losses["chain"]))
     np.testing.assert_allclose(losses["branches"], losses["chain"], rtol=2e-3, atol=2e-3)
+
+
+def test_full_size_sampled_blocks_have_the_sampling_properties():
+    """The sampled workload at its stated size (2,449,029 nodes, 126 M CSR entries, fan-out 15-10-5,
+    1,024 seeds), where the host replay would take minutes: properties that hold whatever the size.
+    Every row of a block holds min(degree, fan-out) distinct neighbours of its node with the graph's
+    weights; the source list starts with the destination nodes and continues with new ids in
+    ascending order; the frontier of the next hop is that source list, padding entries included."""
+    from graph_rws_b200.core.sampling import bcsr_to_csr
+    from graph_rws_b200.data import CSRTopology, synthetic
+    from graph_rws_b200.sampler import BCSRSampler
+    dev = torch.device("cuda")
+    n, e = 2449029, 61_860_000
+    rp, ci, vv = synthetic.chung_lu_csr_torch(n, e, 2.5, 1004, dev)
+    topo = CSRTopology(rp, ci, vv, device=dev, block_dtype=torch.float32)
+    rows_of = torch.repeat_interleave(torch.arange(n, device=dev), rp[1:] - rp[:-1])
+    graph_keys = rows_of * n + ci.long()                  # sorted: rows ascending, columns ascending in a row
+    assert bool((graph_keys[1:] > graph_keys[:-1]).all())
+    deg = (rp[1:] - rp[:-1])
+    seeds = torch.randperm(n, generator=torch.Generator().manual_seed(12))[:1024].to(torch.int32).to(dev)
+    fanouts = [15, 10, 5]
+    blocks = BCSRSampler(fanouts, verbose=False, seed=77, pad_to=256).sample_layers(topo, seeds)
+    assert torch.equal(blocks[-1].output_nodes[:1024], seeds)
+    for b, fanout in zip(blocks, fanouts):               # blocks run input -> output, like the model's layers
+        dst, src = b.output_nodes.long(), b.input_nodes.long()
+        real = dst >= 0                               # a frontier has -1 entries wherever the list above it had them
+        # source list: the destination list as it is, then new ids ascending, then padding
+        assert torch.equal(src[:dst.numel()], dst)
+        tail = src[dst.numel():]
+        n_new = int((tail >= 0).sum())
+        assert bool((tail[:n_new] >= 0).all()) and bool((tail[1:n_new] > tail[:n_new - 1]).all())
+        assert torch.unique(src[src >= 0]).numel() == int((src >= 0).sum()), "a node appears once"
+        # the block's entries as (row, global column, weight)
+        brp, bci, bvv = bcsr_to_csr(b.window_offset, b.original_col_indices, b.values_condensed, dst.numel())
+        cnt = brp[1:] - brp[:-1]
+        want = torch.minimum(deg[dst.clamp(min=0)], torch.tensor(fanout, device=dev))
+        assert torch.equal(cnt, torch.where(real, want, torch.zeros_like(want)))
+        rows = torch.repeat_interleave(torch.arange(dst.numel(), device=dev), cnt)
+        u = src[bci.long()]
+        assert bool((u >= 0).all())
+        keys = dst[rows] * n + u
+        pos = torch.searchsorted(graph_keys, keys)
+        assert bool((graph_keys[pos.clamp(max=graph_keys.numel() - 1)] == keys).all()), "a sampled edge is not in the graph"
+        assert torch.equal(bvv, vv[pos]), "weights are the graph's"
+        # (row, column) pairs are distinct: rows of the CSR view ascend strictly in column id
+        same_row = rows[1:] == rows[:-1]
+        assert bool((bci[1:][same_row] > bci[:-1][same_row]).all())
+    for lower, upper in zip(blocks[1:], blocks[:-1]):     # the frontier of a hop is the source list of the hop above it
+        assert torch.equal(upper.output_nodes, lower.input_nodes)
