@@ -199,13 +199,25 @@ __global__ void __launch_bounds__(WARPS * 32) layer_norm_bwd_kernel(const T *__r
     }
 }
 
-__global__ void layer_norm_param_grad_kernel(const float *__restrict__ partial, int n_partial, int C,
-                                             float *__restrict__ dgamma, float *__restrict__ dbeta) {
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= 2 * C) return;
+// Adds the CTAs' partial rows: a block owns 32 of the 2 C columns, its 32 x 32 threads each take every
+// 32nd partial row (coalesced along the columns), then the 32 sums of a column are added in a fixed
+// order.
+__global__ void __launch_bounds__(1024) layer_norm_param_grad_kernel(const float *__restrict__ partial, int n_partial, int C,
+                                                                      float *__restrict__ dgamma, float *__restrict__ dbeta) {
+    __shared__ float red[32][33];
+    const int cx = threadIdx.x & 31, py = threadIdx.x >> 5;
+    const int c = blockIdx.x * 32 + cx;
     float s = 0.0f;
-    for (int p = 0; p < n_partial; ++p) s += partial[(size_t)p * 2 * C + c];
-    if (c < C) dgamma[c] = s; else dbeta[c - C] = s;
+    if (c < 2 * C)
+        for (int p = py; p < n_partial; p += 32) s += partial[(size_t)p * 2 * C + c];
+    red[py][cx] = s;
+    __syncthreads();
+    if (py == 0 && c < 2 * C) {
+        float t = 0.0f;
+#pragma unroll
+        for (int k = 0; k < 32; ++k) t += red[k][cx];
+        if (c < C) dgamma[c] = t; else dbeta[c - C] = t;
+    }
 }
 
 static int grid_for(int64_t rows) {
@@ -241,7 +253,7 @@ static int launch_bwd(const void *x, const void *gamma, const void *dy, const fl
         layer_norm_bwd_kernel<T, NCH, false><<<g, WARPS * 32, smem, st>>>((const T *)x, (const T *)gamma, (const T *)dy, mean, rstd, (T *)dx, partial, rows, C);
     }
     GRWS_CUDA_TRY(cudaGetLastError());
-    layer_norm_param_grad_kernel<<<(unsigned)ceil_div((int64_t)2 * C, (int64_t)256), 256, 0, st>>>(partial, g, C, dgamma, dbeta);
+    layer_norm_param_grad_kernel<<<(unsigned)ceil_div((int64_t)2 * C, (int64_t)32), 1024, 0, st>>>(partial, g, C, dgamma, dbeta);
     GRWS_CUDA_TRY(cudaGetLastError());
     return GRWS_OK;
 }

@@ -120,9 +120,15 @@ __device__ __forceinline__ uint32_t hash_node(int32_t k) {
 __device__ __forceinline__ uint32_t table_insert(int32_t *keys, uint32_t mask, int32_t key, bool &fresh) {
     uint32_t h = hash_node(key) & mask;
     for (;;) {
-        const int32_t prev = atomicCAS(keys + h, EMPTY_KEY, key);
-        if (prev == EMPTY_KEY) { fresh = true; return h; }
-        if (prev == key) { fresh = false; return h; }
+        // a plain read first: a slot that already holds this key (a hub sampled from many rows) or
+        // another one needs no atomic
+        const int32_t cur = *reinterpret_cast<const volatile int32_t *>(keys + h);
+        if (cur == key) { fresh = false; return h; }
+        if (cur == EMPTY_KEY) {
+            const int32_t prev = atomicCAS(keys + h, EMPTY_KEY, key);
+            if (prev == EMPTY_KEY) { fresh = true; return h; }
+            if (prev == key) { fresh = false; return h; }
+        }
         h = (h + 1) & mask;
     }
 }
@@ -152,12 +158,19 @@ __global__ void insert_dst_kernel(const int32_t *__restrict__ dst, int64_t n_dst
 __global__ void insert_nbr_kernel(const int32_t *__restrict__ nbr, int64_t n_edges, int32_t *keys, int32_t *vals,
                                   uint32_t mask, int32_t *__restrict__ cand, int32_t *__restrict__ n_new) {
     const int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (e >= n_edges) return;
-    const int32_t u = nbr[e];
-    if (u < 0) return;
-    bool fresh;
-    table_insert(keys, mask, u, fresh);
-    if (fresh) cand[atomicAdd(n_new, 1)] = u;    // vals[h] stays NEW_NODE until the ranks are known
+    const int32_t u = e < n_edges ? nbr[e] : -1;
+    bool fresh = false;
+    if (u >= 0) table_insert(keys, mask, u, fresh);
+    // one atomic on the shared counter per warp, not per new node (the order of `cand` does not
+    // matter: it is sorted before the ranks are given out); vals[h] stays NEW_NODE until then
+    const unsigned m = __ballot_sync(0xffffffffu, fresh);
+    if (m) {
+        const int lane = threadIdx.x & 31, leader = __ffs(m) - 1;
+        int base = 0;
+        if (lane == leader) base = atomicAdd(n_new, __popc(m));
+        base = __shfl_sync(0xffffffffu, base, leader);
+        if (fresh) cand[base + __popc(m & ((1u << lane) - 1u))] = u;
+    }
 }
 
 __global__ void rank_new_kernel(const int32_t *__restrict__ cand_sorted, const int32_t *__restrict__ n_new,
