@@ -452,8 +452,14 @@ def run_ours(args):
     secondary = None
     if not args.no_secondary and args.workload == "spmm_mid":
         barrier()
-        secondary = {"gcn_full": secondary_gcn_full(args, torch, scale=args.gcn_scale, steps=args.secondary_steps),
-                     "sampled": secondary_sampled(args, torch, scale=args.sampled_scale, steps=args.secondary_steps)}
+        secondary = {}
+        for name, fn, scale in (("gcn_full", secondary_gcn_full, args.gcn_scale), ("sampled", secondary_sampled, args.sampled_scale)):
+            try:
+                secondary[name] = fn(args, torch, scale=scale, steps=args.secondary_steps)
+            except Exception as exc:          # noqa: BLE001  (a failed secondary line must not take the primary one with it)
+                import traceback
+                traceback.print_exc()
+                secondary[name] = {"error": f"{type(exc).__name__}: {exc}"[:300]}
 
     ok = True
     if rank == 0:
@@ -685,7 +691,10 @@ def secondary_gcn_full(args, torch, scale=1.0, steps=10):
             dist.broadcast(p_.data, 0)
         part = partition_windows_by_tiles(graph.window_offset, world, num_rows=n)
         lo, hi = part.rows(rank)
-        shard = RowShardedGraph.from_full(graph, part, rank, dtype=torch.bfloat16)
+        # all-gathers of the layers (256 and 48 bf16 columns) on the library's own NVLink kernels where the
+        # GPUs can address each other's memory (--nccl-all-gather keeps the collective)
+        shard = RowShardedGraph.from_full(graph, part, rank, dtype=torch.bfloat16,
+                                          peer_row_bytes=0 if getattr(args, 'nccl_all_gather', False) else 512)
         x_l, y_l = x[lo:hi].contiguous(), y[lo:hi].contiguous()
         mine = (train[(train >= lo) & (train < hi)] - lo).contiguous()
         n_train = train.numel()
@@ -734,6 +743,8 @@ def secondary_gcn_full(args, torch, scale=1.0, steps=10):
         eager_step()
     torch.cuda.synchronize()
     coll = collective_timers.stop()
+    if world > 1 and getattr(part, "peer_gather", None) is not None:
+        part.peer_gather.check()          # raises if a wait of an exchange ran out
     ms = torch.tensor([e0.elapsed_time(e1) / steps, coll.get("all_gather", 0.0) / 3, coll.get("all_reduce", 0.0) / 3],
                       dtype=torch.float64, device=device)
     if world > 1:
@@ -743,6 +754,7 @@ def secondary_gcn_full(args, torch, scale=1.0, steps=10):
            "all_gather_ms_per_epoch": float(ms[1]), "all_reduce_ms_per_epoch": float(ms[2]), "host_issue_ms_per_epoch": host_ms,
            "step_mode": step_mode,
            "collective_ms_note": "measured in separate eager epochs with CUDA events around every collective",
+           "all_gather": ("own NVLink kernels (peer loads)" if getattr(part, "peer_gather", None) is not None else "NCCL") if world > 1 else "none",
            "parallelism": "rows x%d, all-gather of H / dY per layer, all-reduce of weight gradients" % world}
     del model, opt
     torch.cuda.empty_cache()
@@ -967,6 +979,7 @@ def main():
     ap.add_argument("--no-secondary", action="store_true", help="SpMM line only")
     ap.add_argument("--no-plan", action="store_true", help="every SpMM launch searches its tile ranges (no per-graph plan)")
     ap.add_argument("--no-ref-gpu", action="store_true")
+    ap.add_argument("--nccl-all-gather", action="store_true", help="gcn_full: NCCL all-gather instead of the library's peer-memory kernels")
     ap.add_argument("--no-pipeline", action="store_true", help="sampled step: sampler and training in one chain, not two branches")
     ap.add_argument("--eager", action="store_true", help="time an eager loop of steps instead of CUDA-graph replays")
     args = ap.parse_args()

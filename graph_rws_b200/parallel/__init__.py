@@ -10,10 +10,12 @@ hot path shards naturally:
   result does not depend on the number of ranks; feature rows of a hop's input nodes are
   fetched from the ranks that own them.
 
-Nothing here issues a TMA multicast load, and no kernel is handed a peer GPU's memory: remote
-rows land in local HBM through the collective first.
+Nothing here issues a TMA multicast load, and no TMA load or library kernel is handed a peer GPU's
+memory: remote rows land in local HBM first, through the collective or through this library's own
+copy kernels (plain loads: ``ShardedFeatures``, ``PeerAllGather``).
 """
 from .row_partition import (RowPartition, all_gather_rows, all_gather_rows_padded, collective_timers,  # noqa: F401
                             partition_windows_by_tiles, shard_bcsr, DistributedSpMM, RowShardedGraph)
 from .seed_shard import exchange_rows, owner_of, shard_seeds  # noqa: F401
 from .feature_store import ShardedFeatures  # noqa: F401,E402
+from .peer_gather import PeerAllGather, make_peer_all_gather  # noqa: F401,E402

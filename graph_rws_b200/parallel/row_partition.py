@@ -145,6 +145,11 @@ def all_gather_rows_padded(local: torch.Tensor, part: RowPartition, group=None) 
     n = local.shape[1]
     if world == 1:
         return local
+    peer = getattr(part, 'peer_gather', None)
+    if peer is not None and local.is_cuda and local.shape[1] * local.element_size() <= peer.max_row_bytes \
+            and (local.shape[1] * local.element_size()) % 16 == 0:
+        with collective_timers.timed("all_gather", local.device):
+            return peer.gather(local)
     send = local
     if local.shape[0] != pad_rows:
         send = torch.empty((pad_rows, n), dtype=local.dtype, device=local.device)
@@ -204,8 +209,14 @@ class RowShardedGraph:
         self._shared = local._shared
 
     @classmethod
-    def from_full(cls, graph, part: RowPartition, rank: int, dtype=None, group=None):
-        """Shard a full graph held by every rank (and its transposed graph) by the same row partition."""
+    def from_full(cls, graph, part: RowPartition, rank: int, dtype=None, group=None, peer_row_bytes: int = 0):
+        """Shard a full graph held by every rank (and its transposed graph) by the same row partition.
+
+        ``peer_row_bytes`` > 0 (the widest dense row that will be exchanged, in bytes): the
+        all-gathers of the products run on the library's own NVLink kernels
+        (``parallel.PeerAllGather``) instead of the NCCL collective, provided the GPUs can address
+        each other's memory and two probe exchanges reproduce the collective; a collective call,
+        every rank must make it."""
         from ..data import BCSRGraph
 
         def shard(g):
@@ -215,6 +226,9 @@ class RowShardedGraph:
                              original_col_indices=cols, values_condensed=vals, device=vals.device,
                              num_rows=hi - lo, num_cols=part.num_rows, values_dtype=vals.dtype)
         gt = graph.transposed(part.num_rows, dtype=dtype or graph.values_condensed.dtype)
+        if peer_row_bytes and part.world > 1 and graph.window_offset.is_cuda and getattr(part, 'peer_gather', None) is None:
+            from .peer_gather import make_peer_all_gather
+            part.peer_gather = make_peer_all_gather(part.max_rows(), int(peer_row_bytes), graph.window_offset.device, group)
         return cls(shard(graph), part, rank, local_t=cls(shard(gt), part, rank, group=group), group=group)
 
     def values_as(self, dtype):

@@ -207,6 +207,28 @@ int grws_block_build_count(const int32_t *local, const float *w, int64_t n_dst, 
                            size_t scratch_bytes, void *stream);
 
 /* ------------------------------------------------------------------------------------------
+ * All-gather of row shards over NVLink with the library's own kernels (the reference is
+ * single-GPU: no counterpart).  Every rank owns a staging block and a control block in memory
+ * that all ranks of the node can address (one symmetric allocation each, mapped into every
+ * rank); `stages` and `ctrl` are DEVICE arrays of `world` pointers to them as this rank sees
+ * them, this rank's own included (`my_stage` is that one again, as a host-side value).  The call
+ * queues two kernels: one copies `local` (local_bytes, the rest of the stage_bytes zero-filled)
+ * into this rank's staging block once every peer has read the previous exchange, the other copies
+ * all ranks' staging blocks into `out` ([world][stage_bytes]) once every rank has published.
+ * `state` is grws_peer_state_bytes() of zero-initialised local device memory that the calls of
+ * one communicator share; the control blocks (grws_peer_ctrl_bytes() each) start zeroed too.
+ * All ranks must make the same sequence of calls with the same stage_bytes.  The waits are
+ * bounded by `wait_limit` SM clocks; a wait that runs out leaves a non-zero status in the
+ * int32 word state[3] (1: peers still reading the previous exchange, 2: peers never published),
+ * `out` is then undefined and the call returns all the same.  No host synchronisation.
+ * ------------------------------------------------------------------------------------------ */
+size_t grws_peer_ctrl_bytes(void);
+size_t grws_peer_state_bytes(void);
+int grws_peer_all_gather(const void *local, int64_t local_bytes, void *my_stage, int64_t stage_bytes,
+                         const void *const *stages, void *const *ctrl, int world, int rank,
+                         void *state, void *out, long long wait_limit, void *stream);
+
+/* ------------------------------------------------------------------------------------------
  * Row normalisation between the graph convolutions: y = LayerNorm(act(x)) * gamma + beta over the
  * C features of every row, act = identity or ReLU (relu_input != 0), and its backward pass.  The
  * reference goes through torch.nn.LayerNorm and a separate activation (models/model.py:117-121).

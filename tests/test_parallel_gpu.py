@@ -87,7 +87,9 @@ def _gcn_worker(rank, world, port, out):
 
         part = partition_windows_by_tiles(graph.window_offset, world, num_rows=n)
         lo, hi = part.rows(rank)
-        shard = RowShardedGraph.from_full(graph, part, rank)
+        # the all-gathers of the layers go through the library's own NVLink kernels (rows of up to 512 bytes)
+        shard = RowShardedGraph.from_full(graph, part, rank, peer_row_bytes=512)
+        assert part.peer_gather is not None, "these GPUs address each other's memory: the peer all-gather must come up"
         mine = train[(train >= lo) & (train < hi)] - lo
         logits = model(shard, X[lo:hi].contiguous())
         assert logits.shape[0] == hi - lo
@@ -98,7 +100,60 @@ def _gcn_worker(rank, world, port, out):
         assert (logits.float() - ref_logits[lo:hi].float()).norm() / ref_logits[lo:hi].float().norm() < 5e-3
         assert abs(float(loss) - float(ref_loss)) < 2e-3 * abs(float(ref_loss))
         assert (grads() - ref_grads).norm() / ref_grads.norm() < 2e-2
+        part.peer_gather.check()
         torch.cuda.synchronize()
+        out[rank] = 1
+    finally:
+        dist.destroy_process_group()
+
+
+def _peer_gather_worker(rank, world, port, out):
+    """parallel.PeerAllGather == all_gather_into_tensor on zero-padded shards: uneven shards, two
+    widths, eagerly and as replays of one CUDA graph with new inputs every time."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from graph_rws_b200.parallel import make_peer_all_gather
+        pad_rows = 4099
+        pg = make_peer_all_gather(pad_rows, 512, dev)
+        assert pg is not None
+        gen = torch.Generator(device=dev).manual_seed(100 + rank)
+
+        def reference(local):
+            send = torch.zeros((pad_rows, local.shape[1]), dtype=local.dtype, device=dev)
+            send[:local.shape[0]] = local
+            want = torch.empty((world * pad_rows, local.shape[1]), dtype=local.dtype, device=dev)
+            dist.all_gather_into_tensor(want, send)
+            return want
+
+        for i, (rows, width, dtype) in enumerate([(pad_rows, 256, torch.bfloat16), (pad_rows - 17 * rank, 48, torch.float16),
+                                                  (pad_rows - 3, 128, torch.float32), (1, 8, torch.float16)]):
+            local = torch.randn((rows, width), generator=gen, device=dev).to(dtype)
+            assert torch.equal(pg.gather(local), reference(local)), f"exchange {i}"
+        # replays of a captured sequence of three exchanges; the inputs change between replays
+        bufs = [torch.zeros((pad_rows - rank, 256), dtype=torch.bfloat16, device=dev),
+                torch.zeros((pad_rows, 48), dtype=torch.bfloat16, device=dev),
+                torch.zeros((pad_rows - 5, 256), dtype=torch.bfloat16, device=dev)]
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            for b in bufs:
+                pg.gather(b)
+        torch.cuda.current_stream(dev).wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            outs = [pg.gather(b) for b in bufs]
+        for step in range(4):
+            for b in bufs:
+                b.copy_(torch.randn(b.shape, generator=gen, device=dev).to(b.dtype))
+            graph.replay()
+            torch.cuda.synchronize()
+            for b, o in zip(bufs, outs):
+                assert torch.equal(o, reference(b)), f"replay {step}"
+        pg.check()
         out[rank] = 1
     finally:
         dist.destroy_process_group()
@@ -191,3 +246,7 @@ def test_row_sharded_gcn_step_matches_single_gpu():
 
 def test_sampled_step_with_features_read_from_peer_memory():
     _run(_sampled_worker)
+
+
+def test_peer_all_gather_matches_the_collective():
+    _run(_peer_gather_worker)
