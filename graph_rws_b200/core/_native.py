@@ -27,6 +27,7 @@ SIGNATURES = {
     "grws_peer_ctrl_bytes": (c_sz, []),
     "grws_peer_state_bytes": (c_sz, []),
     "grws_peer_all_gather": (c_i32, [c_vp, c_i64, c_vp, c_i64, c_vp, c_vp, c_i32, c_i32, c_vp, c_vp, ctypes.c_longlong, c_vp]),
+    "grws_peer_all_gather_push": (c_i32, [c_vp, c_i64, c_i64, c_vp, c_vp, c_i32, c_i32, c_vp, ctypes.c_longlong, c_vp]),
     "grws_layer_norm_scratch_bytes": (c_sz, [c_i64]),
     "grws_layer_norm_fwd": (c_i32, [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_i32, c_i32, ctypes.c_float, c_vp]),
     "grws_layer_norm_bwd": (c_i32, [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_i32, c_i32, c_vp, c_sz, c_vp]),

@@ -19,7 +19,10 @@ class PeerAllGather:
 
     WAIT_LIMIT = 2_000_000_000        # SM clocks, about a second
 
-    def __init__(self, pad_rows: int, max_row_bytes: int, device, group=None):
+    def __init__(self, pad_rows: int, max_row_bytes: int, device, group=None, push: bool = True):
+        """``push``: every rank stores its rows into an inbox on each rank and ``gather`` returns
+        (a view of) this rank's inbox -- valid until the next ``gather``; otherwise every rank
+        publishes its rows in a staging block and pulls everybody's into a fresh tensor."""
         import torch.distributed._symmetric_memory as symm_mem
         lib = _native.lib()
         self.group = group if group is not None else dist.group.WORLD
@@ -27,7 +30,9 @@ class PeerAllGather:
         self.pad_rows, self.max_row_bytes, self.device = int(pad_rows), int(max_row_bytes), torch.device(device)
         if self.max_row_bytes % 16:
             raise ValueError("rows must be a multiple of 16 bytes")
-        self.stage = symm_mem.empty((self.pad_rows * self.max_row_bytes,), dtype=torch.uint8, device=self.device)
+        self.push = bool(push)
+        slots = self.world if self.push else 1
+        self.stage = symm_mem.empty((slots * self.pad_rows * self.max_row_bytes,), dtype=torch.uint8, device=self.device)
         self.ctrl = symm_mem.empty((int(lib.grws_peer_ctrl_bytes()) // 4,), dtype=torch.int32, device=self.device)
         self.ctrl.zero_()
         torch.cuda.synchronize(self.device)
@@ -44,6 +49,12 @@ class PeerAllGather:
         if rows > self.pad_rows or row_bytes > self.max_row_bytes or row_bytes % 16:
             raise ValueError("shard does not fit the staging block")
         local = local.contiguous()
+        if self.push:
+            _native.check(_native.lib().grws_peer_all_gather_push(
+                local.data_ptr(), rows * row_bytes, self.pad_rows * row_bytes, self.stages.data_ptr(), self.ctrls.data_ptr(),
+                self.world, self.rank, self.state.data_ptr(), self.WAIT_LIMIT,
+                torch.cuda.current_stream(self.device).cuda_stream))
+            return self.stage[:self.world * self.pad_rows * row_bytes].view(local.dtype).view(self.world * self.pad_rows, width)
         out = torch.empty((self.world * self.pad_rows, width), dtype=local.dtype, device=self.device)
         _native.check(_native.lib().grws_peer_all_gather(
             local.data_ptr(), rows * row_bytes, self.stage.data_ptr(), self.pad_rows * row_bytes,
@@ -61,7 +72,7 @@ class PeerAllGather:
             raise RuntimeError(f"peer all-gather gave up waiting: {what.get(status, status)}; its output is undefined")
 
 
-def make_peer_all_gather(pad_rows, max_row_bytes, device, group=None, probe_dtype=torch.bfloat16):
+def make_peer_all_gather(pad_rows, max_row_bytes, device, group=None, probe_dtype=torch.bfloat16, push=True):
     """A ``PeerAllGather`` that has reproduced ``all_gather_into_tensor`` on two probe exchanges, or
     None (on every rank alike) when the node's GPUs cannot address each other's memory or a probe
     disagreed -- the caller then keeps the NCCL collective."""
@@ -69,7 +80,7 @@ def make_peer_all_gather(pad_rows, max_row_bytes, device, group=None, probe_dtyp
     ok = 1
     pg = None
     try:
-        pg = PeerAllGather(pad_rows, max_row_bytes, device, group)
+        pg = PeerAllGather(pad_rows, max_row_bytes, device, group, push=push)
     except Exception:                      # noqa: BLE001  (no symmetric memory on this box)
         ok = 0
     flag = torch.tensor([ok], device=device)

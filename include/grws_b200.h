@@ -227,6 +227,14 @@ size_t grws_peer_state_bytes(void);
 int grws_peer_all_gather(const void *local, int64_t local_bytes, void *my_stage, int64_t stage_bytes,
                          const void *const *stages, void *const *ctrl, int world, int rank,
                          void *state, void *out, long long wait_limit, void *stream);
+/* The push form of the same exchange: every rank owns an inbox of [world][stage_bytes] in symmetric
+ * memory (`inboxes`: device array of `world` pointers); the call stores this rank's rows into slot
+ * `rank` of every inbox once all ranks are done with the previous contents, and when its kernels
+ * have run this rank's inbox holds the gathered operand -- until this rank's next call.  One pass
+ * over the data instead of two, and stores over the links instead of loads. */
+int grws_peer_all_gather_push(const void *local, int64_t local_bytes, int64_t stage_bytes,
+                              void *const *inboxes, void *const *ctrl, int world, int rank,
+                              void *state, long long wait_limit, void *stream);
 
 /* ------------------------------------------------------------------------------------------
  * Row normalisation between the graph convolutions: y = LayerNorm(act(x)) * gamma + beta over the

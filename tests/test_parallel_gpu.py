@@ -117,46 +117,50 @@ def _peer_gather_worker(rank, world, port, out):
     try:
         from graph_rws_b200.parallel import make_peer_all_gather
         pad_rows = 4099
-        pg = make_peer_all_gather(pad_rows, 512, dev)
-        assert pg is not None
         gen = torch.Generator(device=dev).manual_seed(100 + rank)
-
-        def reference(local):
-            send = torch.zeros((pad_rows, local.shape[1]), dtype=local.dtype, device=dev)
-            send[:local.shape[0]] = local
-            want = torch.empty((world * pad_rows, local.shape[1]), dtype=local.dtype, device=dev)
-            dist.all_gather_into_tensor(want, send)
-            return want
-
-        for i, (rows, width, dtype) in enumerate([(pad_rows, 256, torch.bfloat16), (pad_rows - 17 * rank, 48, torch.float16),
-                                                  (pad_rows - 3, 128, torch.float32), (1, 8, torch.float16)]):
-            local = torch.randn((rows, width), generator=gen, device=dev).to(dtype)
-            assert torch.equal(pg.gather(local), reference(local)), f"exchange {i}"
-        # replays of a captured sequence of three exchanges; the inputs change between replays
-        bufs = [torch.zeros((pad_rows - rank, 256), dtype=torch.bfloat16, device=dev),
-                torch.zeros((pad_rows, 48), dtype=torch.bfloat16, device=dev),
-                torch.zeros((pad_rows - 5, 256), dtype=torch.bfloat16, device=dev)]
-        side = torch.cuda.Stream(dev)
-        side.wait_stream(torch.cuda.current_stream(dev))
-        with torch.cuda.stream(side):
-            for b in bufs:
-                pg.gather(b)
-        torch.cuda.current_stream(dev).wait_stream(side)
-        torch.cuda.synchronize()
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            outs = [pg.gather(b) for b in bufs]
-        for step in range(4):
-            for b in bufs:
-                b.copy_(torch.randn(b.shape, generator=gen, device=dev).to(b.dtype))
-            graph.replay()
-            torch.cuda.synchronize()
-            for b, o in zip(bufs, outs):
-                assert torch.equal(o, reference(b)), f"replay {step}"
-        pg.check()
+        for push in (True, False):
+            _peer_gather_checks(make_peer_all_gather(pad_rows, 512, dev, push=push), pad_rows, world, rank, dev, gen)
         out[rank] = 1
     finally:
         dist.destroy_process_group()
+
+
+def _peer_gather_checks(pg, pad_rows, world, rank, dev, gen):
+    assert pg is not None
+
+    def reference(local):
+        send = torch.zeros((pad_rows, local.shape[1]), dtype=local.dtype, device=dev)
+        send[:local.shape[0]] = local
+        want = torch.empty((world * pad_rows, local.shape[1]), dtype=local.dtype, device=dev)
+        dist.all_gather_into_tensor(want, send)
+        return want
+
+    for i, (rows, width, dtype) in enumerate([(pad_rows, 256, torch.bfloat16), (pad_rows - 17 * rank, 48, torch.float16),
+                                              (pad_rows - 3, 128, torch.float32), (1, 8, torch.float16)]):
+        local = torch.randn((rows, width), generator=gen, device=dev).to(dtype)
+        assert torch.equal(pg.gather(local), reference(local)), f"exchange {i}"
+    # replays of a captured sequence of three exchanges; the inputs change between replays
+    bufs = [torch.zeros((pad_rows - rank, 256), dtype=torch.bfloat16, device=dev),
+            torch.zeros((pad_rows, 48), dtype=torch.bfloat16, device=dev),
+            torch.zeros((pad_rows - 5, 256), dtype=torch.bfloat16, device=dev)]
+    side = torch.cuda.Stream(dev)
+    side.wait_stream(torch.cuda.current_stream(dev))
+    with torch.cuda.stream(side):
+        for b in bufs:
+            pg.gather(b)
+    torch.cuda.current_stream(dev).wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        outs = [pg.gather(b).clone() for b in bufs]      # (the push form returns its inbox: valid until the next exchange)
+    for step in range(4):
+        for b in bufs:
+            b.copy_(torch.randn(b.shape, generator=gen, device=dev).to(b.dtype))
+        graph.replay()
+        torch.cuda.synchronize()
+        for b, o in zip(bufs, outs):
+            assert torch.equal(o, reference(b)), f"replay {step}"
+    pg.check()
 
 
 def _sampled_worker(rank, world, port, out):
