@@ -66,5 +66,7 @@ def build_selftest(force: bool = False) -> str:
 
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
-    if "--selftest" in sys.argv:
+    # the self-test build shares every object but one with the product: it is kept in step with it
+    # (a variant build under another name, GRWS_LIB_NAME, has no self-test twin)
+    if "--selftest" in sys.argv or (os.path.exists(SELFTEST_LIB) and "GRWS_LIB_NAME" not in os.environ):
         print(build_selftest(force="--force" in sys.argv))
