@@ -561,6 +561,7 @@ def cpu_baseline(csr, H_host, G_host, bytes_step, budget_s=12.0):
     port = nbytes / best / 1e9
     ts_gbs, ts_s, ts_threads = torch_sparse_cpu(csr, H_host, G_host, bytes_step)
     return {"value": max(port, ts_gbs), "unit": "GB/s", "cores": oracle.num_threads(), "kind": "port",
+            "fastest": "torch.sparse" if ts_gbs > port else "port",     # which of the two `value` is
             "port_gbs": port, "torch_sparse_gbs": ts_gbs, "torch_sparse_s_per_step": ts_s, "torch_sparse_threads": ts_threads,
             "sample": "whole workload (forward + transposed product), best of %d steps in %.1f s, %.3f s per step (port); "
                       "torch.sparse CSR fp32 %.3f s per step" % (len(times), time.perf_counter() - t_start, best, ts_s)}
