@@ -755,7 +755,8 @@ def secondary_gcn_full(args, torch, scale=1.0, steps=10):
            "all_gather_ms_per_epoch": float(ms[1]), "all_reduce_ms_per_epoch": float(ms[2]), "host_issue_ms_per_epoch": host_ms,
            "step_mode": step_mode,
            "collective_ms_note": "measured in separate eager epochs with CUDA events around every collective",
-           "all_gather": ("own NVLink kernels (stores into peer memory)" if getattr(part, "peer_gather", None) is not None else "NCCL") if world > 1 else "none",
+           "all_gather": ("own NVLink kernels (stores into peer memory)" if getattr(part, "peer_gather", None) is not None
+                          else "NCCL (faster than the peer kernels in the set-up probe, or no peer access)") if world > 1 else "none",
            "parallelism": "rows x%d, all-gather of H / dY per layer, all-reduce of weight gradients" % world}
     del model, opt
     torch.cuda.empty_cache()

@@ -72,10 +72,12 @@ class PeerAllGather:
             raise RuntimeError(f"peer all-gather gave up waiting: {what.get(status, status)}; its output is undefined")
 
 
-def make_peer_all_gather(pad_rows, max_row_bytes, device, group=None, probe_dtype=torch.bfloat16, push=True):
-    """A ``PeerAllGather`` that has reproduced ``all_gather_into_tensor`` on two probe exchanges, or
-    None (on every rank alike) when the node's GPUs cannot address each other's memory or a probe
-    disagreed -- the caller then keeps the NCCL collective."""
+def make_peer_all_gather(pad_rows, max_row_bytes, device, group=None, probe_dtype=torch.bfloat16, push=True,
+                         keep_if_slower=False):
+    """A ``PeerAllGather`` that has reproduced ``all_gather_into_tensor`` on two probe exchanges and
+    is not slower than it on the widest operand (unless ``keep_if_slower``), or None (on every rank
+    alike) when the node's GPUs cannot address each other's memory, a probe disagreed or the
+    collective was faster -- the caller then keeps the NCCL collective."""
     group = group if group is not None else dist.group.WORLD
     ok = 1
     pg = None
@@ -101,5 +103,27 @@ def make_peer_all_gather(pad_rows, max_row_bytes, device, group=None, probe_dtyp
         flag = torch.tensor([1 if same else 0], device=device)
         dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
         if int(flag) == 0:
+            return None
+    if not keep_if_slower:
+        # which of the two is faster depends on the number of ranks and the links: time both on
+        # the widest operand (slowest rank counts) and keep the collective if it wins
+        local = torch.randn((pad_rows, width), generator=gen, device=device).to(probe_dtype)
+        want = torch.empty((pg.world * pad_rows, width), dtype=probe_dtype, device=device)
+        times = []
+        for fn in (lambda: pg.gather(local), lambda: dist.all_gather_into_tensor(want, local, group=group)):
+            for _ in range(2):
+                fn()
+            dist.barrier(group)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(5):
+                fn()
+            b.record()
+            b.synchronize()
+            times.append(a.elapsed_time(b))
+        t = torch.tensor(times, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+        pg.probe_ms = (float(t[0]) / 5, float(t[1]) / 5)          # (peer kernels, collective) per exchange
+        if float(t[0]) > float(t[1]):
             return None
     return pg

@@ -88,8 +88,10 @@ def _gcn_worker(rank, world, port, out):
         part = partition_windows_by_tiles(graph.window_offset, world, num_rows=n)
         lo, hi = part.rows(rank)
         # the all-gathers of the layers go through the library's own NVLink kernels (rows of up to 512 bytes)
-        shard = RowShardedGraph.from_full(graph, part, rank, peer_row_bytes=512)
+        from graph_rws_b200.parallel import make_peer_all_gather
+        part.peer_gather = make_peer_all_gather(part.max_rows(), 512, dev, keep_if_slower=True)
         assert part.peer_gather is not None, "these GPUs address each other's memory: the peer all-gather must come up"
+        shard = RowShardedGraph.from_full(graph, part, rank, peer_row_bytes=512)
         mine = train[(train >= lo) & (train < hi)] - lo
         logits = model(shard, X[lo:hi].contiguous())
         assert logits.shape[0] == hi - lo
@@ -119,7 +121,7 @@ def _peer_gather_worker(rank, world, port, out):
         pad_rows = 4099
         gen = torch.Generator(device=dev).manual_seed(100 + rank)
         for push in (True, False):
-            _peer_gather_checks(make_peer_all_gather(pad_rows, 512, dev, push=push), pad_rows, world, rank, dev, gen)
+            _peer_gather_checks(make_peer_all_gather(pad_rows, 512, dev, push=push, keep_if_slower=True), pad_rows, world, rank, dev, gen)
         out[rank] = 1
     finally:
         dist.destroy_process_group()
